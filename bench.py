@@ -41,6 +41,31 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "tflops_burst": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
 
 
+def ncu_traffic(key):
+    """DRAM traffic figures come from ncu captures, not from the timed run: they are kept as data beside the
+    capture summaries, each with the hash of the kernel's source file at capture time. Returns (entry, stale):
+    stale is True when the source has changed since (the figure then needs a new capture), None when the capture
+    predates the hash record."""
+    import hashlib
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            entry = json.load(f).get(key)
+    except Exception:
+        return None, None
+    if not entry:
+        return None, None
+    stale = None
+    try:
+        with open(os.path.join(ROOT, entry["source"]), "rb") as f:
+            now = hashlib.sha256(f.read()).hexdigest()[:16]
+        if entry.get("source_sha16_at_capture"):
+            stale = now != entry["source_sha16_at_capture"]
+    except Exception:
+        pass
+    return entry, stale
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -117,16 +142,21 @@ def cpu_encoder_generic(cfg, seconds_budget=20.0):
 def cpu_encoder_blas(cfg, batch=4, reps=1):
     """The same op sequence with every matrix product in multi-threaded BLAS sgemm (stand-in for the MKL build)."""
     from oracle import oracle_np as ON
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=os.cpu_count() or 1)
+    except Exception:
+        pass
     x = cfg["x"][:batch]
     lens = cfg["lengths"][:batch]
     ON.encoder(x[:1], cfg["layers"][:1], cfg["heads"], lens[:1], dtype=np.float32)
-    best = None
+    best, out = None, None
     for _ in range(reps):
         t0 = time.perf_counter()
-        ON.encoder(x, cfg["layers"], cfg["heads"], lens, dtype=np.float32)
+        out = ON.encoder(x, cfg["layers"], cfg["heads"], lens, dtype=np.float32)
         dt = time.perf_counter() - t0
         best = dt if best is None else min(best, dt)
-    return best, x.shape[0] * x.shape[1] / best
+    return best, x.shape[0] * x.shape[1] / best, out
 
 
 def run_reference(args):
@@ -136,6 +166,12 @@ def run_reference(args):
         return
     from dl4s_b200 import workloads
     cores = os.cpu_count() or 1
+    # The launcher of multi-rank runs exports OMP_NUM_THREADS=1; the CPU arm is one process and takes every core.
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=cores)
+    except Exception:
+        pass
     cfg = workloads.encoder_config()
     batch = 4
     times = []
@@ -193,6 +229,13 @@ class Gpu:
         assert self.stream.cuda_stream != 0
         cuda.set_stream(self.stream.cuda_stream)
         self.flush_buf = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
+        # The library's own communicator (NCCL behind the C ABI) for the head-sharded layer. torch.distributed only
+        # carries the 128-byte id from rank 0 to the others, the barriers and the max-over-ranks of the timings.
+        if self.world > 1:
+            from dl4s_b200 import sharded
+            box = [sharded.comm_unique_id() if self.rank == 0 else None]
+            self.dist.broadcast_object_list(box, src=0)
+            sharded.comm_init(self.rank, self.world, box[0])
 
     def barrier(self):
         if self.dist is not None:
@@ -212,6 +255,13 @@ class Gpu:
             return x
         t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def min_over_ranks(self, x: float) -> float:
+        if self.dist is None:
+            return x
+        t = self.torch.tensor([x], dtype=self.torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MIN)
         return float(t.item())
 
     def timed_steps(self, step, steps, warmup, flush=True):
@@ -302,11 +352,12 @@ def attention_prefill_bench(gpu, peaks, B=4, H=16, S=8192, d=128, reps=5, prec=N
            "tflops_call": flops / (total_ms * 1e-3) / 1e12}
     if ms_kernel:
         ach = flops / (ms_kernel * 1e-3) / 1e12
+        # captured on a smaller case (the capture-size rule); the traffic grows with the element count B*H*S*d
+        tr, stale = ncu_traffic("k_attn_prefill_tc")
         res["roofline"] = {"bound": "tensor", "kernel": "k_attn_prefill_tc", "achieved": ach, "peak": peaks["tflops_burst"],
                            "unit": "TFLOP/s", "frac": ach / peaks["tflops_burst"],
-                           # ncu capture of B2 H8 S4096 d128 (profiles/attn_prefill_tc_*.md): 53.4 MB of DRAM traffic for
-                           # 16.8 M (b,h,s,d) elements; traffic grows with that element count.
-                           "traffic": 53.37e6 * (B * H * S * d) / (2 * 8 * 4096 * 128),
+                           "traffic": tr["bytes"] * (B * H * S * d) / tr["units_captured"] if tr else None,
+                           "traffic_source": {"capture": tr["summary"], "kernel_source_changed_since_capture": stale} if tr else None,
                            "peak_source": peaks["source"] + " bf16 dense burst (half operands run at the same rate)",
                            "ms_kernel": ms_kernel}
     return res
@@ -342,11 +393,12 @@ def attention_decode_bench(gpu, peaks, B=64, H=32, L=4096, d=128, reps=10):
            "ms_call": total_ms, "gbs_call": bytes_alg / (total_ms * 1e-3) / 1e9}
     if ms_kernel:
         ach = bytes_alg / (ms_kernel * 1e-3) / 1e9
+        tr, stale = ncu_traffic("k_attn_decode_partial")   # captured at a quarter of the batch: a ratio to the algorithmic bytes
         res["roofline"] = {"bound": "hbm", "kernel": "k_attn_decode_partial", "achieved": ach, "peak": peaks["hbm_gbs"],
                            "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                           # ncu capture of B16 (profiles/attn_decode_partial_*.md): DRAM traffic = 1.003 x algorithmic bytes
-                           "traffic": 1.003 * bytes_alg, "peak_source": peaks["source"],
-                           "ms_kernel": ms_kernel}
+                           "traffic": tr["ratio_to_algorithmic"] * bytes_alg if tr else None,
+                           "traffic_source": {"capture": tr["summary"], "kernel_source_changed_since_capture": stale} if tr else None,
+                           "peak_source": peaks["source"], "ms_kernel": ms_kernel}
     # spot check against the slab: the same (h) slab serves every batch row, so rows with equal length agree
     return res
 
@@ -355,7 +407,7 @@ def run_encoder(args, gpu, peaks):
     from dl4s_b200 import PREC_F16, PREC_FP32, workloads
     from dl4s_b200.layers import TransformerEncoder
     cuda = gpu.cuda
-    prec = PREC_FP32 if args.precision == "fp32" else PREC_F16
+    prec = precision_of(args)
     cfg = workloads.encoder_config(seed_ids=1 + gpu.rank, seed_len=3 + gpu.rank)
     B, S, D = cfg["x"].shape
     H, F, L = cfg["heads"], cfg["F"], len(cfg["layers"])
@@ -457,6 +509,19 @@ def run_encoder(args, gpu, peaks):
     e2e_matches = bool(np.array_equal(host_result, out.numpy())) if (state["i"] - 1) % 2 == 0 else bool(
         np.array_equal(host_result, outs[1].numpy()))
     nbytes_h2d = int(ids_host.nbytes + lens_host.nbytes)
+    # the read-back alone (no kernels running): what the host link gives one rank while every rank copies at once
+    gpu.sync()
+    gpu.barrier()
+    d0, d1 = gpu.event(), gpu.event()
+    d0.record(copy_stream)
+    for i in range(args.steps):
+        call("dl4s_cuda_memcpy_d2h_async_on", houts[i % 2], c_vp(outs[i % 2].ptr), out_bytes, c_vp(copy_stream.cuda_stream))
+    d1.record(copy_stream)
+    gpu.sync()
+    d2h_only_ms = d0.elapsed_time(d1) / args.steps
+    d2h_only_gbs = out_bytes / (d2h_only_ms * 1e-3) / 1e9
+    d2h_only_gbs_min = gpu.min_over_ranks(d2h_only_gbs)
+    d2h_only_ms_max = gpu.max_over_ranks(d2h_only_ms)
 
     # ---- per-kernel profile of the same step, and the roofline of the dominant kernel
     gpu.flush_l2()
@@ -485,17 +550,20 @@ def run_encoder(args, gpu, peaks):
             alg = L * 2 * (3 * B * S * D * 4)      # two LayerNorms per layer, read twice + write once
             unit, peak, bound = "GB/s", peaks["hbm_gbs"], "hbm"
             ach = alg / (ms_dom * 1e-3) / 1e9
-        # DRAM bytes of the 24 GEMM launches of one step, from an ncu pass over this same command
-        # (profiles/encoder_step_launch_list.md); other kernels were not captured.
-        traffic = 1.452e9 if ("gemm" in dom and (B, S, D, F, L) == (32, 512, 512, 2048, 6)) else None
+        # DRAM bytes of the GEMM launches of one step come from an ncu pass over this same command (single-rounded
+        # weights, this exact configuration); other kernels and modes were not captured.
+        tr, stale = ncu_traffic("k_gemm_tc.encoder_step")
+        use = tr and "gemm" in dom and (B, S, D, F, L) == (32, 512, 512, 2048, 6) and args.precision == "f16"
+        traffic = tr["bytes"] if use else None
         roof = {"bound": bound, "kernel": dom, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak, "traffic": traffic,
+                "traffic_source": {"capture": tr["summary"], "kernel_source_changed_since_capture": stale} if use else None,
                 "launches_per_step": prof[dom]["launches"], "ms_per_step": ms_dom,
                 "peak_source": peaks["source"], "share_of_step": ms_dom / max(sum(v["total_ms"] for v in prof.values()), 1e-9)}
 
     line = {
         "metric": "encoder_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": gpu.world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32 in/out; f16 tensor-core operands, f32 accumulate" if prec == PREC_F16 else "f32",
+        "vs_baseline": None, "dtype": DTYPE_NOTE[args.precision],
         "data": "synthetic",
         "config": {"workload": "transformer_encoder_prefill", "layers": L, "d_model": D, "heads": H, "d_ff": F,
                    "batch_per_gpu": B, "global_batch": B * gpu.world, "seq_len": S, "mask": "padding, lengths U[256,512]",
@@ -506,15 +574,30 @@ def run_encoder(args, gpu, peaks):
         "gpu_launches": launches, "gpu_launches_per_step": launches_per_step,
         "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": nbytes_h2d,
                 "d2h_bytes_per_step": int(out_bytes), "ms_per_step": e2e_ms / args.steps, "result_finite": finite,
+                "d2h_only": {"ms_per_step_max_over_ranks": d2h_only_ms_max, "gbs_per_gpu_min_over_ranks": d2h_only_gbs_min,
+                             "gbs_all_gpus": d2h_only_gbs_min * gpu.world,
+                             "note": "the same read-back with no kernels running, all ranks copying at once: when this is "
+                                     "longer than the device step, the host link bounds the end-to-end rate"},
                 "result_matches_device": e2e_matches,
                 "path": "ids + lengths from pinned host memory, embedding + positional encoding and the encoder on the "
                         "device, states read back into pinned host memory on a second stream under the next step"},
         "clocks": clocks, "roofline": roof,
         "kernel_profile_ms_per_step": {k: round(v["total_ms"], 4) for k, v in prof_detail.items()},
     }
+    if not args.no_head_sharded:
+        # the layer that spans GPUs (heads over ranks, one all-gather per batch chunk), at every N including 1
+        first_rows = out.numpy()[:4] if (gpu.rank == 0 and gpu.world == 1) else None
+        line["head_sharded"] = head_sharded_bench(args, gpu, peaks, steps=max(3, min(args.steps, 10)))
+    else:
+        first_rows = out.numpy()[:4] if (gpu.rank == 0 and gpu.world == 1) else None
     if gpu.rank == 0 and gpu.world == 1:
         line["cpu_baseline"] = cpu_encoder_generic(cfg)
-        blas_dt, blas_tps = cpu_encoder_blas(cfg)
+        blas_dt, blas_tps, blas_out = cpu_encoder_blas(cfg)
+        err = first_rows.astype(np.float64) - blas_out
+        line["cpu_baseline"]["agreement_with_gpu"] = {
+            "max_abs": float(np.abs(err).max()), "rel_l2": float(np.linalg.norm(err) / np.linalg.norm(blas_out)),
+            "sample": "the 4 sequences of the BLAS run, GPU output of the timed configuration against the CPU output",
+            "stated_tolerance": "max-abs 2e-3, relative L2 1e-3 (tensor-core paths); 1e-5 (fp32)"}
         line["cpu_baseline"]["blas_value"] = blas_tps
         line["cpu_baseline"]["blas_cores"] = os.cpu_count()
         line["cpu_baseline"]["blas_sample"] = f"4 of 32 sequences x 6 layers in {blas_dt:.2f} s, multi-threaded BLAS sgemm"
@@ -525,19 +608,29 @@ def run_encoder(args, gpu, peaks):
     return line
 
 
-def run_decoder_mha(args, gpu, peaks):
+def precision_of(args):
+    from dl4s_b200 import PREC_F16, PREC_F16_SPLIT, PREC_FP32
+    return {"fp32": PREC_FP32, "f16": PREC_F16, "f16_split": PREC_F16_SPLIT}[args.precision]
+
+
+DTYPE_NOTE = {"fp32": "f32", "f16": "f32 in/out; f16 tensor-core operands, f32 accumulate",
+              "f16_split": "f32 in/out; f16 tensor-core operands with weights as two halves (hi + lo), f32 accumulate"}
+
+
+def head_sharded_bench(args, gpu, peaks, shape=None, steps=None, warmup=3):
     """Head-sharded TransformerDecoder self-attention block (MultiHeadAttention with a causal mask): batch 256,
-    seq 2048, d_model 4096, 32 heads. Heads are split over the ranks, ONE NCCL all-gather of the head outputs
-    precedes Wo, the second half runs per batch slice. Total work is fixed: strong scaling."""
+    seq 2048, d_model 4096, 32 heads. Heads are split over the ranks, ONE ncclAllGather of the head outputs per batch
+    chunk precedes Wo (issued by the library, dl4s_cuda_mha_forward_sharded), the second half runs per batch slice.
+    Total work is fixed: strong scaling. Returns the measurements as a dict (every rank calls this; collectives)."""
     import torch
-    from dl4s_b200 import PREC_F16, PREC_FP32
+    from dl4s_b200 import sharded
     from dl4s_b200.cuda import ShapedBuffer
     from dl4s_b200.layers import xavier_uniform
-    from dl4s_b200.sharded import HeadShardedMultiHeadAttention
     cuda = gpu.cuda
-    B, S, D, H = [int(v) for v in args.shape.split(",")] if args.shape else (256, 2048, 4096, 32)
+    B, S, D, H = shape or (256, 2048, 4096, 32)
+    steps = steps or args.steps
     dk = D // H
-    prec = PREC_FP32 if args.precision == "fp32" else PREC_F16
+    prec = precision_of(args)
     rw = np.random.default_rng(0)
     weights = {n: xavier_uniform(rw, D, D) for n in ("qDense", "kDense", "vDense", "fc")}
     # X ~ N(0,1): 8.6 GB at full size, replicated on every rank; drawn on the device from a fixed seed
@@ -546,7 +639,7 @@ def run_decoder_mha(args, gpu, peaks):
     gen.manual_seed(1)
     xt = torch.randn((B, S, D), generator=gen, device="cuda", dtype=torch.float32)
     x = ShapedBuffer(xt.data_ptr(), (B, S, D), owned=False)
-    layer = HeadShardedMultiHeadAttention(H, D, dk, dk, weights, precision=prec, chunks=args.chunks)
+    layer = sharded.HeadShardedMultiHeadAttention(H, D, dk, dk, weights, precision=prec, chunks=args.chunks)
     mask = cuda.StructuredMask(None, causal=True)
     owned = layer.owned_batches(B)
     out_t = torch.empty((max(len(owned), 1), S, D), device="cuda", dtype=torch.float32)
@@ -557,11 +650,14 @@ def run_decoder_mha(args, gpu, peaks):
 
     sampler = ClockSampler(gpu.local)
     sampler.start()
-    total_ms = gpu.timed_steps(step, args.steps, args.warmup, flush=False)
+    total_ms = gpu.timed_steps(step, steps, warmup, flush=False)
     launches = gpu.last_timed_launches
     clocks = sampler.stop()
+    # the collective: device time of the gathers of one step and the part the compute stream waited for (max over ranks)
+    step()
+    gather_ms, exposed_ms = sharded.comm_timing()
+    gather_ms, exposed_ms = gpu.max_over_ranks(gather_ms), gpu.max_over_ranks(exposed_ms)
     flops = 3 * 2 * B * S * D * D + 4 * B * H * dk * (S * (S + 1) // 2) + 2 * B * S * D * D
-    tokens = B * S * args.steps
     cuda.profile_begin()
     step()
     prof = cuda.profile_end()
@@ -571,17 +667,44 @@ def run_decoder_mha(args, gpu, peaks):
     check = out_t[:len(owned)].abs().sum(dtype=torch.float64).reshape(1)
     if gpu.dist is not None:
         gpu.dist.all_reduce(check)
-    return {"metric": "decoder_self_attention_tokens_per_s", "value": tokens / (total_ms * 1e-3), "unit": "tokens/s",
-            "n_gpus": gpu.world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "f32 in/out; f16 tensor-core operands, f32 accumulate" if prec == PREC_F16 else "f32", "data": "synthetic",
-            "config": {"workload": "head_sharded_decoder_self_attention", "batch": B, "seq_len": S, "d_model": D, "heads": H,
-                       "mask": "causal", "parallelism": f"heads over {gpu.world} GPU(s), one all-gather before Wo per batch chunk ({layer.chunks} chunk(s), "
-                                                        "gather of a chunk under the next chunk's compute), output by batch slice",
-                       "l2": "inputs (8.6 GB) exceed L2; no flush"},
-            "tflops": flops * args.steps / (total_ms * 1e-3) / 1e12, "gpu_launches": launches, "clocks": clocks,
-            "kernel_profile_ms_per_step": {k: round(v["total_ms"], 3) for k, v in prof.items()}, "sample_output": first,
-            "output_abs_sum": float(check.item())}
+    ms = total_ms / steps
+    esz = 4 if args.precision == "fp32" else 2
+    sent = B * S * (D // gpu.world) * esz
+    res = {"workload": "head_sharded_decoder_self_attention", "batch": B, "seq_len": S, "d_model": D, "heads": H, "mask": "causal",
+           "n_gpus": gpu.world, "steps": steps, "warmup": warmup, "scaling": "strong", "ms_per_step": ms,
+           "tokens_per_s": B * S / (ms * 1e-3), "tflops": flops / (ms * 1e-3) / 1e12,
+           "tflops_per_gpu_frac_of_sustained_peak": flops / (ms * 1e-3) / 1e12 / gpu.world / peaks["tflops_sustained"],
+           "collective": {"call": "ncclAllGather, in place, issued by dl4s_cuda_mha_forward_sharded on a second stream",
+                          "per_step": layer.chunks if gpu.world > 1 else 0, "chunks": layer.chunks,
+                          "bytes_sent_per_gpu": sent if gpu.world > 1 else 0,
+                          "bytes_received_per_gpu": sent * (gpu.world - 1),
+                          "element": "f16" if esz == 2 else "f32", "nccl_version": sharded.comm_info()[2],
+                          "gather_ms_per_step": gather_ms, "exposed_ms_per_step": exposed_ms,
+                          "hidden_ms_per_step": max(gather_ms - exposed_ms, 0.0)},
+           "gpu_launches": launches, "clocks": clocks, "precision": args.precision,
+           "kernel_profile_ms_per_step": {k: round(v["total_ms"], 3) for k, v in prof.items()}, "sample_output": first,
+           "output_abs_sum": float(check.item()), "l2": "inputs (8.6 GB) exceed L2; no flush"}
+    del layer, out_t, xt
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_decoder_mha(args, gpu, peaks):
+    """`--workload decoder_mha`: the head-sharded layer as the line's own metric."""
+    shape = tuple(int(v) for v in args.shape.split(",")) if args.shape else None
+    r = head_sharded_bench(args, gpu, peaks, shape=shape, warmup=args.warmup)
+    return {"metric": "decoder_self_attention_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s",
+            "n_gpus": gpu.world, "steps": r["steps"], "warmup": r["warmup"], "ms_per_step": r["ms_per_step"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE_NOTE[args.precision],
+            "data": "synthetic",
+            "config": {"workload": r["workload"], "batch": r["batch"], "seq_len": r["seq_len"], "d_model": r["d_model"],
+                       "heads": r["heads"], "mask": "causal",
+                       "parallelism": f"heads over {gpu.world} GPU(s), one all-gather before Wo per batch chunk "
+                                      f"({r['collective']['chunks']} chunk(s), gather of a chunk under the next chunk's compute), "
+                                      "output by batch slice", "l2": r["l2"]},
+            "tflops": r["tflops"], "gpu_launches": r["gpu_launches"], "clocks": r["clocks"], "collective": r["collective"],
+            "kernel_profile_ms_per_step": r["kernel_profile_ms_per_step"], "sample_output": r["sample_output"],
+            "output_abs_sum": r["output_abs_sum"]}
 
 
 def run_mha_small(args, gpu, peaks):
@@ -800,8 +923,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="encoder", choices=["encoder", "prefill", "decode", "decoder_mha", "gemm", "mha", "decode_step", "head"])
-    ap.add_argument("--precision", default="f16", choices=["f16", "fp32"])
+    ap.add_argument("--precision", default="f16", choices=["f16", "f16_split", "fp32"],
+                    help="f16: half operands rounded once; f16_split: weights as two halves (meets max-abs 2e-3 on the 6-layer "
+                         "encoder); fp32: FFMA check kernels")
     ap.add_argument("--no-attention", action="store_true", help="skip the attention-only sections of the default line")
+    ap.add_argument("--no-head-sharded", action="store_true", help="skip the head-sharded layer section of the default line")
     ap.add_argument("--no-graph", action="store_true", help="encoder workload: launch the kernels eagerly instead of replaying "
                                                             "a captured CUDA graph")
     ap.add_argument("--chunks", type=int, default=4, help="decoder_mha on more than one GPU: batch chunks whose all-gather "
@@ -834,7 +960,10 @@ def main():
     if gpu.rank == 0:
         print(json.dumps(line), flush=True)
     if gpu.dist is not None:
+        from dl4s_b200 import sharded
+        gpu.sync()
         gpu.dist.barrier()
+        sharded.comm_destroy()
         gpu.dist.destroy_process_group()
 
 

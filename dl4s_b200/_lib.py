@@ -22,6 +22,7 @@ c_sz = ctypes.c_size_t
 
 PREC_FP32 = 0
 PREC_F16 = 1
+PREC_F16_SPLIT = 2
 ACT_GELU_SIGMOID = 0
 ACT_RELU = 1
 
@@ -38,6 +39,9 @@ _SIGNATURES = {
     "dl4s_cuda_device_status": [c_i32p],
     "dl4s_cuda_set_timing": [c_i32],
     "dl4s_cuda_get_timing": [c_f32p],
+    "dl4s_cuda_set_trace": [c_i32],
+    "dl4s_cuda_trace_read": [ctypes.c_char_p, c_sz],
+    "dl4s_cuda_inject_failure": [c_i32, c_i32],
     "dl4s_cuda_launch_count": [ctypes.POINTER(ctypes.c_uint64)],
     "dl4s_cuda_graph_begin": [],
     "dl4s_cuda_graph_end": [ctypes.POINTER(c_vp)],
@@ -82,6 +86,8 @@ _SIGNATURES = {
     "dl4s_cuda_reduce_max": [c_vp, c_i64p, c_i32, c_i32p, c_i32, c_vp, c_vp],
     "dl4s_cuda_permute_axes": [c_vp, c_i64p, c_i32, c_i32p, c_vp],
     "dl4s_cuda_stack": [ctypes.POINTER(c_vp), c_i64p, c_i32, c_i32, c_i32, c_vp],
+    "dl4s_cuda_unstack": [c_vp, ctypes.POINTER(c_vp), c_i64p, c_i32, c_i32, c_i32],
+    "dl4s_cuda_unstack_add": [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_i64p, c_i32, c_i32, c_i32],
     "dl4s_cuda_band": [c_vp, c_i64, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp],
     "dl4s_cuda_gemm": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_f32, c_f32, c_i32, c_i32, c_i32],
     "dl4s_cuda_sdpa_forward": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f32, c_vp, c_i32,
@@ -98,6 +104,14 @@ _SIGNATURES = {
     "dl4s_cuda_mha_heads_half_supported": [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i32p],
     "dl4s_cuda_mha_output_forward": [c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_i32, c_i32, c_i64,
                                      c_i64],
+    "dl4s_cuda_comm_unique_id": [c_vp],
+    "dl4s_cuda_comm_init": [c_i32, c_i32, c_vp],
+    "dl4s_cuda_comm_destroy": [],
+    "dl4s_cuda_comm_info": [c_i32p, c_i32p, c_i32p],
+    "dl4s_cuda_comm_timing": [c_f32p, c_f32p],
+    "dl4s_cuda_mha_forward_sharded": [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32,
+                                      c_vp, c_i32, c_i32],
+    "dl4s_cuda_mha_sharded_plan": [c_i64, c_i32, c_i32, c_i32, c_i64p, c_i64p],
     "dl4s_cuda_mha_decode_step": [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64,
                                   c_vp, c_vp],
     "dl4s_cuda_output_head": [c_vp, c_i64, c_i64, c_vp, c_i64, c_vp, c_vp, c_i32],
@@ -105,6 +119,10 @@ _SIGNATURES = {
     "dl4s_cuda_ffn_forward": [c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_i32],
     "dl4s_cuda_encoder_forward": [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_i32,
                                   c_vp, c_i32],
+    "dl4s_cuda_encoder_prepare": [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_i32, ctypes.POINTER(c_vp)],
+    "dl4s_cuda_encoder_prepared_refresh": [c_vp],
+    "dl4s_cuda_encoder_prepared_destroy": [c_vp],
+    "dl4s_cuda_encoder_forward_prepared": [c_vp, c_vp, c_i64, c_i64, c_vp, c_i32, c_vp],
     "dl4s_cuda_embed_positional": [c_vp, c_i64, c_i64, c_i64, c_vp, c_i64, c_i32, c_vp],
 }
 _SPECIAL = {

@@ -3,7 +3,10 @@
 
 #include <cstdlib>
 
+#include <atomic>
 #include <mutex>
+
+#include <nvtx3/nvToolsExt.h>
 
 namespace dl4s {
 
@@ -51,7 +54,7 @@ dl4s_status arena_reserve(DeviceState *st, size_t bytes, void **ptr)
                         "captured: run the same calls once before dl4s_cuda_graph_begin", bytes, st->arena_bytes);
         // Everything that used the old arena was enqueued before this call.
         DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
-        if (st->arena) DL4S_CUDA_TRY(cudaFree(st->arena));
+        DL4S_TRY(release_internal(st, st->arena));
         st->arena = nullptr;
         st->arena_bytes = 0;
         size_t want = align_up(bytes + bytes / 8, (size_t)1 << 20);
@@ -60,6 +63,59 @@ dl4s_status arena_reserve(DeviceState *st, size_t bytes, void **ptr)
     }
     *ptr = st->arena;
     return DL4S_OK;
+}
+
+dl4s_status release_internal(DeviceState *st, void *ptr)
+{
+    if (!ptr) return DL4S_OK;
+    if (st->live_graphs > 0) {
+        // A graph recorded earlier replays kernels that read and write this buffer.
+        if (st->n_retired == kMaxRetired)
+            return fail(DL4S_ERR_UNSUPPORTED, "%d internal buffers are already kept alive for recorded graphs: destroy the graphs "
+                        "(dl4s_cuda_graph_destroy) before running larger shapes", kMaxRetired);
+        st->retired[st->n_retired++] = ptr;
+        return DL4S_OK;
+    }
+    DL4S_CUDA_TRY(cudaFree(ptr));
+    return DL4S_OK;
+}
+
+static std::atomic<int> g_inject[8];
+
+bool take_injected_failure(int what)
+{
+    if (what < 1 || what >= 8) return false;
+    int n = g_inject[what].load();
+    while (n > 0) {
+        if (g_inject[what].compare_exchange_weak(n, n - 1)) return true;
+    }
+    return false;
+}
+
+void trace_push(DeviceState *st, const char *name)
+{
+    nvtxRangePushA(name);
+    if (st->trace_depth < 16) st->trace_stack[st->trace_depth] = name;
+    st->trace_depth++;
+    if (!st->trace_log) return;
+    // append the path "A/B/C\n" if it fits
+    size_t need = 1;
+    const int depth = st->trace_depth < 16 ? st->trace_depth : 16;
+    for (int i = 0; i < depth; ++i) need += strlen(st->trace_stack[i]) + 1;
+    if (st->trace_len + need >= kTraceLogBytes) return;
+    for (int i = 0; i < depth; ++i) {
+        size_t n = strlen(st->trace_stack[i]);
+        memcpy(st->trace_log + st->trace_len, st->trace_stack[i], n);
+        st->trace_len += n;
+        st->trace_log[st->trace_len++] = (i + 1 < depth) ? '/' : '\n';
+    }
+    st->trace_log[st->trace_len] = 0;
+}
+
+void trace_pop(DeviceState *st)
+{
+    nvtxRangePop();
+    if (st->trace_depth > 0) st->trace_depth--;
 }
 
 void profile_record(DeviceState *st, const char *name)
@@ -92,9 +148,19 @@ static dl4s_status init_one(int ordinal)
     DL4S_CUDA_TRY(cudaEventCreate(&d.ev0));
     DL4S_CUDA_TRY(cudaEventCreate(&d.ev1));
     d.launches = 0;
+    // The no-allocation decode entry point must find its array and kernels resident: take them now.
+    DL4S_TRY(decode_static_prepare(&d));
     {
         const char *e = getenv("DL4S_PDL");
         d.pdl = !(e && e[0] == '0');
+        // DL4S_CUDA_TRACE=1: operation-group ranges from the start (see dl4s_cuda_set_trace)
+        const char *t = getenv("DL4S_CUDA_TRACE");
+        if (t && t[0] == '1') {
+            d.trace_log = new char[kTraceLogBytes];
+            d.trace_log[0] = 0;
+            d.trace_len = 0;
+            d.tracing = true;
+        }
     }
     d.live = true;
     return DL4S_OK;
@@ -142,7 +208,9 @@ dl4s_status dl4s_cuda_shutdown(void)
         if (!d.live) continue;
         cudaSetDevice(d.ordinal);
         cudaStreamSynchronize(d.stream);
+        comm_release_device(d.ordinal);
         if (d.arena) cudaFree(d.arena);
+        for (int r = 0; r < d.n_retired; ++r) cudaFree(d.retired[r]);
         if (d.status_word) cudaFree(d.status_word);
         if (d.ln_partials) cudaFree(d.ln_partials);
         if (d.tile_counters) cudaFree(d.tile_counters);
@@ -151,6 +219,7 @@ dl4s_status dl4s_cuda_shutdown(void)
         cudaEventDestroy(d.ev0);
         cudaEventDestroy(d.ev1);
         cudaStreamDestroy(d.own_stream);
+        delete[] d.trace_log;
         d = DeviceState();
     }
     t_current = -1;
@@ -208,8 +277,12 @@ dl4s_status dl4s_cuda_device_status(int32_t *status_word)
     DL4S_CUDA_TRY(cudaMemsetAsync(st->status_word, 0, sizeof(w), st->stream));
     DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
     if (status_word) *status_word = w;
-    if (w & 0x200) return fail(DL4S_ERR_INVALID_ARG, "a decode step found its key/value cache full (status word 0x%x)", w);
-    if (w != 0) return fail(DL4S_ERR_TIMEOUT, "a bounded device-side wait gave up (status word 0x%x)", w);
+    if (w & kStatusTimeoutMask) return fail(DL4S_ERR_TIMEOUT, "a bounded device-side wait gave up (status word 0x%x)", w);
+    if (w & kStatusCacheFull) return fail(DL4S_ERR_INVALID_ARG, "a decode step found its key/value cache full (status word 0x%x)", w);
+    if (w & kStatusHalfRange)
+        return fail(DL4S_ERR_INVALID_ARG, "a tensor-core operand left the IEEE half range (|x| >= 65504 or not finite): the results of "
+                    "the calls since the last status read are not usable (status word 0x%x)", w);
+    if (w != 0) return fail(DL4S_ERR_CUDA, "unknown device status word 0x%x", w);
     return DL4S_OK;
 }
 
@@ -268,6 +341,7 @@ dl4s_status dl4s_cuda_graph_end(void **graph)
         return check_cuda(e, "cudaGraphInstantiate");
     }
     *graph = h;
+    st->live_graphs++;
     return DL4S_OK;
 }
 
@@ -289,7 +363,21 @@ dl4s_status dl4s_cuda_graph_destroy(void *graph)
     if (!h) return DL4S_OK;
     if (h->exec) cudaGraphExecDestroy(h->exec);
     if (h->graph) cudaGraphDestroy(h->graph);
+    const int device = h->device;
     delete h;
+    // With the last graph of a device gone nothing names the retired internal buffers any more.
+    if (device >= 0 && device < kMaxDevices && g_dev[device].live) {
+        DeviceState &d = g_dev[device];
+        if (d.live_graphs > 0 && --d.live_graphs == 0 && d.n_retired > 0) {
+            int prev = -1;
+            cudaGetDevice(&prev);
+            cudaSetDevice(d.ordinal);
+            cudaStreamSynchronize(d.stream);   // a replay may still be running
+            for (int r = 0; r < d.n_retired; ++r) cudaFree(d.retired[r]);
+            d.n_retired = 0;
+            if (prev >= 0) cudaSetDevice(prev);
+        }
+    }
     return DL4S_OK;
 }
 
@@ -341,6 +429,38 @@ dl4s_status dl4s_cuda_profile_end(char *report, size_t capacity)
     return DL4S_OK;
 }
 
+dl4s_status dl4s_cuda_inject_failure(int32_t what, int32_t count)
+{
+    if (what < 1 || what >= 8) return fail(DL4S_ERR_INVALID_ARG, "unknown failure kind %d", what);
+    g_inject[what].store(count > 0 ? count : 0);
+    return DL4S_OK;
+}
+
+dl4s_status dl4s_cuda_set_trace(int32_t enable)
+{
+    DL4S_STATE(st);
+    if (enable && !st->trace_log) {
+        st->trace_log = new char[kTraceLogBytes];
+        st->trace_log[0] = 0;
+        st->trace_len = 0;
+    }
+    st->tracing = enable != 0;
+    return DL4S_OK;
+}
+
+dl4s_status dl4s_cuda_trace_read(char *report, size_t capacity)
+{
+    DL4S_STATE(st);
+    DL4S_REQUIRE(report && capacity > 0, "no room for the report");
+    size_t n = st->trace_log ? st->trace_len : 0;
+    if (n >= capacity) n = capacity - 1;
+    if (n) memcpy(report, st->trace_log, n);
+    report[n] = 0;
+    st->trace_len = 0;
+    if (st->trace_log) st->trace_log[0] = 0;
+    return DL4S_OK;
+}
+
 dl4s_status dl4s_cuda_launch_count(uint64_t *count)
 {
     DL4S_STATE(st);
@@ -352,6 +472,10 @@ dl4s_status dl4s_cuda_launch_count(uint64_t *count)
 
 dl4s_status dl4s_cuda_malloc(size_t bytes, void **d_ptr)
 {
+    if (take_injected_failure(DL4S_INJECT_MALLOC)) {
+        if (d_ptr) *d_ptr = nullptr;
+        return fail(DL4S_ERR_OOM, "injected failure: allocation of %zu bytes refused (dl4s_cuda_inject_failure)", bytes);
+    }
     DL4S_STATE(st);
     DL4S_REQUIRE(d_ptr, "d_ptr is NULL");
     *d_ptr = nullptr;
@@ -372,6 +496,8 @@ dl4s_status dl4s_cuda_free(void *d_ptr)
 
 dl4s_status dl4s_cuda_memcpy_h2d(void *d_dst, const void *src, size_t bytes)
 {
+    if (take_injected_failure(DL4S_INJECT_H2D))
+        return fail(DL4S_ERR_CUDA, "injected failure: host-to-device copy of %zu bytes refused (dl4s_cuda_inject_failure)", bytes);
     DL4S_STATE(st);
     DL4S_REQUIRE(bytes == 0 || (d_dst && src), "NULL pointer");
     DL4S_CUDA_TRY(cudaMemcpyAsync(d_dst, src, bytes, cudaMemcpyHostToDevice, st->stream));
@@ -382,6 +508,8 @@ dl4s_status dl4s_cuda_memcpy_h2d(void *d_dst, const void *src, size_t bytes)
 
 dl4s_status dl4s_cuda_memcpy_h2d_async(void *d_dst, const void *src, size_t bytes)
 {
+    if (take_injected_failure(DL4S_INJECT_H2D))
+        return fail(DL4S_ERR_CUDA, "injected failure: host-to-device copy of %zu bytes refused (dl4s_cuda_inject_failure)", bytes);
     DL4S_STATE(st);
     DL4S_REQUIRE(bytes == 0 || (d_dst && src), "NULL pointer");
     DL4S_CUDA_TRY(cudaMemcpyAsync(d_dst, src, bytes, cudaMemcpyHostToDevice, st->stream));

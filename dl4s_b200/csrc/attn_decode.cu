@@ -34,6 +34,7 @@ __global__ void __launch_bounds__(DEC_THREADS) k_attn_decode_partial(const float
     const int split = blockIdx.x;
     const int64_t h = blockIdx.y, b = blockIdx.z, bh = b * H + h;
     int64_t len = lens ? lens[b] : Lmax;
+    if (len > Lmax) len = Lmax;       // a length beyond the buffers reads what exists, as the other attention kernels do
     const bool uniform = (len <= 0);  // every key blocked: the reference's finite -1e9 gives equal weights
     if (uniform) len = Lmax;
     const int64_t begin = (int64_t)split * chunk;
@@ -209,6 +210,22 @@ static dl4s_status static_decode_scratch(DeviceState *st, float **ptr)
     return DL4S_OK;
 }
 
+// Called by dl4s_cuda_init with the device current: looks the array's address up and makes the driver load the
+// decode kernels now. With lazy module loading the array and the kernels would otherwise be brought onto the
+// device by the first decode call, which is exactly when a host that has since claimed all of HBM cannot spare
+// the 8 MiB.
+dl4s_status decode_static_prepare(DeviceState *st)
+{
+    float *p = nullptr;
+    DL4S_TRY(static_decode_scratch(st, &p));
+    cudaFuncAttributes attr;
+    DL4S_CUDA_TRY(cudaFuncGetAttributes(&attr, k_attn_decode_partial<128>));
+    DL4S_CUDA_TRY(cudaFuncGetAttributes(&attr, k_attn_decode_partial<64>));
+    DL4S_CUDA_TRY(cudaFuncGetAttributes(&attr, k_attn_decode_merge<128>));
+    DL4S_CUDA_TRY(cudaFuncGetAttributes(&attr, k_attn_decode_merge<64>));
+    return DL4S_OK;
+}
+
 }  // namespace dl4s
 
 using namespace dl4s;
@@ -219,7 +236,8 @@ extern "C" dl4s_status dl4s_cuda_sdpa_decode_noalloc(const float *d_q, const flo
 {
     DL4S_STATE(st);
     DL4S_REQUIRE(d_q && d_k && d_v && d_out, "NULL buffer");
-    DL4S_REQUIRE(B >= 1 && H >= 1 && Lmax >= 1, "bad extents");
+    DL4S_REQUIRE(B >= 0 && H >= 0 && Lmax >= 1, "bad extents");
+    if (B * H == 0) return DL4S_OK;   // nothing to do, as in dl4s_cuda_sdpa_decode
     DL4S_REQUIRE(d == 64 || d == 128, "the no-allocation decode handles head size 64 or 128 (got %lld)", (long long)d);
     DL4S_REQUIRE(temperature != 0.0f, "temperature must not be zero");
     DL4S_REQUIRE(B <= 65535 && H <= 65535, "B and H must each be at most 65535");
@@ -238,6 +256,7 @@ extern "C" dl4s_status dl4s_cuda_sdpa_decode_noalloc(const float *d_q, const flo
                     (long long)(B * H * nsplit * (d + 2)), kStaticDecodeFloats);
     float *scratch = nullptr;
     DL4S_TRY(static_decode_scratch(st, &scratch));
+    ScopedTimer timer(st);
     return launch_attn_decode(st, d_q, d_k, d_v, B, H, Lmax, d, d, 1.0f / temperature, d_key_lengths, d_out, scratch, chunk,
                               nsplit);
 }

@@ -476,7 +476,7 @@ __global__ void __launch_bounds__(at_threads(NT), NT == 2 ? 1 : 2) k_attn_prefil
     // Common exit, also reached after a wait that gave up.
     tc_fence_before();
     __syncthreads();
-    if (threadIdx.x == 0 && abort_s) atomicOr(p.status, 0x200);
+    if (threadIdx.x == 0 && abort_s) atomicOr(p.status, kStatusAttnTimeout);
     if (warp == W_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
@@ -578,16 +578,16 @@ dl4s_status launch_attn_prefill_tc_h(DeviceState *st, const void *qh, const void
     return run_attn_tc<64, 1>(st, tq, tk, tv, p, BH);
 }
 
-size_t tc_layer_scratch_bytes(int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk, int64_t dv, int64_t F)
+size_t tc_layer_scratch_bytes(int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk, int64_t dv, int64_t F, int split)
 {
     size_t m = 0;
     auto upd = [&](size_t v) { if (v > m) m = v; };
     int64_t M = B * S;
-    upd(gemm_tc_scratch_bytes(M, H * dk, D));
-    upd(gemm_tc_scratch_bytes(M, H * dv, D));
-    upd(gemm_tc_scratch_bytes(M, D, H * dv));
+    upd(gemm_tc_scratch_bytes(M, H * dk, D, split));
+    upd(gemm_tc_scratch_bytes(M, H * dv, D, split));
+    upd(gemm_tc_scratch_bytes(M, D, H * dv, split));
     upd(attn_prefill_tc_scratch_bytes(B, H, S, S, dk, dv));
-    if (F > 0) { upd(gemm_tc_scratch_bytes(M, F, D)); upd(gemm_tc_scratch_bytes(M, D, F)); }
+    if (F > 0) { upd(gemm_tc_scratch_bytes(M, F, D, split)); upd(gemm_tc_scratch_bytes(M, D, F, split)); }
     return m;
 }
 

@@ -16,6 +16,7 @@ namespace dl4s {
 constexpr int kMaxDevices = 16;
 constexpr int kLnPartialSlots = 1 << 20;   // 16 MB: one pair of sums per 32 rows x column part of the largest fused-statistics product
 constexpr int kTileCounterSlots = 64;
+constexpr int kMaxRetired = 64;            // internal buffers kept for live graphs, see DeviceState::retired
 
 // Per-device state. The scratch arena is grow-only and reused by every fused
 // call on the device's stream (stream order makes reuse safe).
@@ -42,6 +43,13 @@ struct DeviceState {
     // allocate or wait may happen in between.
     bool capturing = false;
     uint64_t launches_at_capture_begin = 0;
+    // Graphs returned by dl4s_cuda_graph_end and not yet destroyed. Their kernels hold the addresses of the
+    // internal buffers (arena, skinny_partials, pe_table) as they were at capture time, so while any graph
+    // lives a buffer that has to grow is retired (kept allocated) instead of freed; the retired buffers go
+    // when the last graph is destroyed.
+    int live_graphs = 0;
+    void *retired[kMaxRetired] = {};
+    int n_retired = 0;
     // Sinusoidal positional-encoding table [pe_rows, pe_dim], built on first use and kept.
     float *pe_table = nullptr;
     int64_t pe_rows = 0, pe_dim = 0;
@@ -50,6 +58,12 @@ struct DeviceState {
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_ms = 0.f;
+    // Operation-group trace (dl4s_cuda_set_trace): NVTX ranges + a host-side list of the group paths entered.
+    bool tracing = false;
+    int trace_depth = 0;
+    const char *trace_stack[16] = {};
+    char *trace_log = nullptr;      // kTraceLogBytes, newline-separated "A/B/C" paths
+    size_t trace_len = 0;
     // Per-kernel profile (dl4s_cuda_profile_begin/end): one event after every launch.
     bool profiling = false;
     int prof_n = 0;                       // launches recorded; event prof_n closes the last one
@@ -57,6 +71,22 @@ struct DeviceState {
     const char **prof_names = nullptr;
 };
 constexpr int kMaxProfileLaunches = 4096;
+constexpr size_t kTraceLogBytes = 1 << 16;
+
+// The operation groups of the reference (OperationGroup.capture(named:), Tensor/Graph.swift:134-163: "Encoder",
+// "EncoderLayer", "MultiHeadAttention", "ScaledDotProductAttention", "PointwiseFeedForward", "LayerNorm", ...) as
+// NVTX ranges around the launches they cover, when tracing is on.
+void trace_push(DeviceState *st, const char *name);
+void trace_pop(DeviceState *st);
+struct ScopedGroup {
+    DeviceState *st;
+    ScopedGroup(DeviceState *s, const char *name) : st(s) { if (st->tracing) trace_push(st, name); }
+    ~ScopedGroup() { if (st->tracing) trace_pop(st); }
+};
+
+// Failure injection for tests (dl4s_cuda_inject_failure): true when a pending injected failure of kind `what` was
+// consumed by this call.
+bool take_injected_failure(int what);
 void profile_record(DeviceState *st, const char *name);
 
 DeviceState *current();                 // nullptr (and last error set) when not initialised
@@ -64,6 +94,8 @@ dl4s_status fail(dl4s_status code, const char *fmt, ...);
 dl4s_status check_cuda(cudaError_t e, const char *what);
 // Returns a pointer to at least `bytes` of device scratch (256-byte aligned).
 dl4s_status arena_reserve(DeviceState *st, size_t bytes, void **ptr);
+// Frees an internal buffer that is being replaced, or keeps it for the graphs that still name its address.
+dl4s_status release_internal(DeviceState *st, void *ptr);
 
 #define DL4S_CUDA_TRY(expr)                                            \
     do {                                                               \
@@ -111,6 +143,34 @@ struct ScopedTimer {
         }
     }
 };
+
+// ---- device status word (read and cleared by dl4s_cuda_device_status) ----
+// 0x001-0x100: a bounded wait of a tensor-core kernel gave up; 0x200: a decode step found its cache full;
+// 0x400: a value became infinite (or was not finite to begin with) when the tensor-core path rounded it to IEEE
+// half, i.e. an operand outside |x| < 65504.
+constexpr int32_t kStatusAttnTimeout = 0x080;   // k_attn_prefill_tc
+constexpr int32_t kStatusGemmTimeout = 0x100;   // k_gemm_tc
+constexpr int32_t kStatusTimeoutMask = 0x1FF;
+constexpr int32_t kStatusCacheFull = 0x200;
+constexpr int32_t kStatusHalfRange = 0x400;
+#ifdef __CUDACC__
+// True when either half of a packed half2 has all exponent bits set (inf or NaN).
+__device__ __forceinline__ bool half2_not_finite(uint32_t h)
+{
+    return ((h & 0x7C00u) == 0x7C00u) | ((h & 0x7C000000u) == 0x7C000000u);
+}
+// Four floats as packed halves (hi) and the packed half-rounded remainders v - hi (lo).
+__device__ __forceinline__ void split_hilo(const float4 &v, uint2 &hi, uint2 &lo)
+{
+    const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+    const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+    const __half2 l0 = __floats2half2_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2half2_rn(v.z - f1.x, v.w - f1.y);
+    hi.x = *reinterpret_cast<const uint32_t *>(&h0);
+    hi.y = *reinterpret_cast<const uint32_t *>(&h1);
+    lo.x = *reinterpret_cast<const uint32_t *>(&l0);
+    lo.y = *reinterpret_cast<const uint32_t *>(&l1);
+}
+#endif
 
 // ---- programmatic dependent launch ----
 // Kernels of one pipeline are launched with the programmatic-serialization attribute: the next kernel's CTAs may
@@ -183,6 +243,12 @@ dl4s_status launch_attn_decode(DeviceState *st, const float *q, const float *k, 
                                int64_t H, int64_t Lmax, int64_t dk, int64_t dv, float inv_temperature,
                                const int32_t *d_key_lengths, float *out, float *scratch, int64_t chunk,
                                int64_t nsplit);
+
+// comm.cu: frees a device's communicator, second stream and gather buffers.
+void comm_release_device(int ordinal);
+
+// Resolves the fixed split-K array of dl4s_cuda_sdpa_decode_noalloc and loads the decode kernels (device current).
+dl4s_status decode_static_prepare(DeviceState *st);
 
 // gemm_f32.cu — C = alpha*op(A)op(B) + beta*C with a fused epilogue.
 enum Epilogue { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_BIAS_RELU = 3, EPI_BIAS_RESIDUAL = 4, EPI_RESIDUAL = 5 };

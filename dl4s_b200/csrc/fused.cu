@@ -64,7 +64,7 @@ __global__ void __launch_bounds__(128) k_kv_append(const float *__restrict__ k_n
     if (len < 0) len = 0;
     if (len >= Lmax) {
         if (threadIdx.x == 0) {
-            atomicOr(status, 0x200);
+            atomicOr(status, kStatusCacheFull);
             if (h == 0) len1[b] = (int32_t)Lmax;
         }
         return;
@@ -77,6 +77,11 @@ __global__ void __launch_bounds__(128) k_kv_append(const float *__restrict__ k_n
     for (int64_t i = threadIdx.x; i < dk; i += blockDim.x) kd[i] = ks[i];
     for (int64_t i = threadIdx.x; i < dv; i += blockDim.x) vd[i] = vs[i];
 }
+
+// DL4S_PREC_F16 and DL4S_PREC_F16_SPLIT both run on the tensor cores; the second keeps weights as two halves.
+static inline bool prec_known(int p) { return p == DL4S_PREC_FP32 || p == DL4S_PREC_F16 || p == DL4S_PREC_F16_SPLIT; }
+static inline bool prec_tc(int p) { return p == DL4S_PREC_F16 || p == DL4S_PREC_F16_SPLIT; }
+static inline int prec_split(int p) { return p == DL4S_PREC_F16_SPLIT ? 1 : 0; }
 
 static dl4s_status check_mask(const MaskSpec &m, int64_t B, int64_t H, int64_t Sq, int64_t Sk)
 {
@@ -103,9 +108,10 @@ static dl4s_status attention(DeviceState *st, const float *q, Strides4 qs, const
                              Strides4 vs, float *o, Strides4 os, int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk,
                              int64_t dv, float inv_t, const MaskSpec &mask, int precision, void *scratch, size_t scratch_bytes)
 {
+    ScopedGroup group(st, "ScaledDotProductAttention");
     // The tensor-core kernel covers structural masks and head sizes 64 / 128; everything
     // else (dense masks, odd head sizes) runs on the fp32 kernel, which is the more exact one.
-    if (precision == DL4S_PREC_F16 && !mask.d_mask && attn_prefill_tc_supported(Sq, Sk, dk, dv))
+    if (prec_tc(precision) && !mask.d_mask && attn_prefill_tc_supported(Sq, Sk, dk, dv))
         return launch_attn_prefill_tc(st, q, qs, k, ks, v, vs, o, os, B, H, Sq, Sk, dk, dv, inv_t, mask, scratch, scratch_bytes);
     return launch_attn_ref(st, q, qs, k, ks, v, vs, o, os, B, H, Sq, Sk, dk, dv, inv_t, mask);
 }
@@ -113,8 +119,8 @@ static dl4s_status attention(DeviceState *st, const float *q, Strides4 qs, const
 static dl4s_status gemm(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K, int epi,
                         const float *bias, const float *residual, int precision, void *scratch, size_t scratch_bytes)
 {
-    if (precision == DL4S_PREC_F16 && gemm_tc_supported(M, N, K))
-        return launch_gemm_tc(st, a, b, c, M, N, K, epi, bias, residual, scratch, scratch_bytes);
+    if (prec_tc(precision) && gemm_tc_supported(M, N, K))
+        return launch_gemm_tc(st, a, b, c, M, N, K, epi, bias, residual, scratch, scratch_bytes, prec_split(precision));
     return launch_gemm_f32(st, a, b, c, M, N, K, 1.0f, 0.0f, 0, 0, epi, bias, residual);
 }
 
@@ -142,6 +148,7 @@ static dl4s_status mha_heads(DeviceState *st, const float *xq, const float *xk, 
                              const float *wq, const float *wk, const float *wv, const MaskSpec &mask, float *heads_out,
                              int precision, float *ws, void *extra, size_t extra_bytes)
 {
+    ScopedGroup group(st, "MultiHeadAttention");
     float *qp = ws;
     float *kp = qp + s.B * s.Sq * s.H * s.dk;
     float *vp = kp + s.B * s.Sk * s.H * s.dk;
@@ -183,6 +190,7 @@ static dl4s_status ffn(DeviceState *st, const float *x, int64_t M, int64_t D, in
                        const float *w2, const float *b2, const float *g, const float *sh, int act, float *out, int precision,
                        float *ws, void *extra, size_t extra_bytes)
 {
+    ScopedGroup group(st, "PointwiseFeedForward");
     float *hbuf = ws;
     float *obuf = hbuf + M * F;
     int epi1 = act == DL4S_ACT_RELU ? EPI_BIAS_RELU : EPI_BIAS_GELU;
@@ -204,11 +212,12 @@ dl4s_status dl4s_cuda_gemm(const float *d_a, const float *d_b, float *d_c, int64
     DL4S_REQUIRE(M >= 0 && N >= 0 && K >= 0, "negative extent");
     DL4S_REQUIRE(M * N == 0 || (d_c && (K == 0 || (d_a && d_b))), "NULL buffer");
     ScopedTimer timer(st);
-    if (precision == DL4S_PREC_F16 && !trans_a && !trans_b && alpha == 1.0f && beta == 0.0f && gemm_tc_supported(M, N, K)) {
-        size_t need = gemm_tc_scratch_bytes(M, N, K);
+    DL4S_REQUIRE(prec_known(precision), "unknown precision %d", precision);
+    if (prec_tc(precision) && !trans_a && !trans_b && alpha == 1.0f && beta == 0.0f && gemm_tc_supported(M, N, K)) {
+        size_t need = gemm_tc_scratch_bytes(M, N, K, prec_split(precision));
         void *scratch = nullptr;
         DL4S_TRY(arena_reserve(st, need, &scratch));
-        return launch_gemm_tc(st, d_a, d_b, d_c, M, N, K, EPI_NONE, nullptr, nullptr, scratch, need);
+        return launch_gemm_tc(st, d_a, d_b, d_c, M, N, K, EPI_NONE, nullptr, nullptr, scratch, need, prec_split(precision));
     }
     return launch_gemm_f32(st, d_a, d_b, d_c, M, N, K, alpha, beta, trans_a, trans_b, EPI_NONE, nullptr, nullptr);
 }
@@ -224,13 +233,13 @@ dl4s_status dl4s_cuda_sdpa_forward(const float *d_q, const float *d_k, const flo
     DL4S_REQUIRE(temperature != 0.0f, "temperature must not be zero");
     DL4S_REQUIRE(!d_mask || mask_shape, "a dense mask needs its shape");
     DL4S_REQUIRE(!causal || Sq == Sk, "the causal mask of DL4S is square (TransformerUtil.swift:38-50): Sq must equal Sk");
-    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16, "unknown precision %d", precision);
+    DL4S_REQUIRE(prec_known(precision), "unknown precision %d", precision);
     MaskSpec mask = make_mask(d_key_lengths, causal, d_mask, mask_shape);
     DL4S_TRY(check_mask(mask, B, H, Sq, Sk));
     ScopedTimer timer(st);
     void *scratch = nullptr;
     size_t need = 0;
-    if (precision == DL4S_PREC_F16) {
+    if (prec_tc(precision)) {
         need = attn_prefill_tc_scratch_bytes(B, H, Sq, Sk, dk, dv);
         DL4S_TRY(arena_reserve(st, need, &scratch));
     }
@@ -321,17 +330,18 @@ dl4s_status dl4s_cuda_mha_forward(const float *d_xq, const float *d_xk, const fl
     DL4S_REQUIRE(B >= 1 && Sq >= 1 && Sk >= 1 && D >= 1 && H >= 1 && dk >= 1 && dv >= 1, "bad extents");
     DL4S_REQUIRE(!d_mask || mask_shape, "a dense mask needs its shape");
     DL4S_REQUIRE(!causal || Sq == Sk, "the causal mask of DL4S is square: Sq must equal Sk");
-    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16, "unknown precision %d", precision);
+    DL4S_REQUIRE(prec_known(precision), "unknown precision %d", precision);
     MaskSpec mask = make_mask(d_key_lengths, causal, d_mask, mask_shape);
     DL4S_TRY(check_mask(mask, B, H, Sq, Sk));
     MhaShape s{B, Sq, Sk, D, H, dk, dv};
-    if (precision == DL4S_PREC_F16 && d_xq == d_xk && d_xk == d_xv && !d_mask && tc_block_supported(B, Sq, Sk, D, H, dk, dv, 0)) {
+    if (prec_tc(precision) && d_xq == d_xk && d_xk == d_xv && !d_mask && tc_block_supported(B, Sq, Sk, D, H, dk, dv, 0)) {
         // Self-attention: the fused tensor-core pipeline (one q/k/v product, half intermediates).
         ScopedTimer timer(st);
-        return mha_self_tc(st, d_xq, B, Sq, D, H, dk, dv, d_wq, d_wk, d_wv, d_wo, d_ln_scale, d_ln_shift, mask, d_out);
+        return mha_self_tc(st, d_xq, B, Sq, D, H, dk, dv, d_wq, d_wk, d_wv, d_wo, d_ln_scale, d_ln_shift, mask, d_out,
+                           prec_split(precision));
     }
     size_t main_bytes = align_up(mha_scratch_floats(s) * sizeof(float), 1024);
-    size_t extra = precision == DL4S_PREC_F16 ? tc_layer_scratch_bytes(B, Sq > Sk ? Sq : Sk, D, H, dk, dv, 0) : 0;
+    size_t extra = prec_tc(precision) ? tc_layer_scratch_bytes(B, Sq > Sk ? Sq : Sk, D, H, dk, dv, 0, prec_split(precision)) : 0;
     void *base = nullptr;
     DL4S_TRY(arena_reserve(st, main_bytes + extra, &base));
     ScopedTimer timer(st);
@@ -348,18 +358,19 @@ dl4s_status dl4s_cuda_mha_heads_forward(const float *d_xq, const float *d_xk, co
     DL4S_REQUIRE(d_xq && d_xk && d_xv && d_wq && d_wk && d_wv && d_heads_out, "NULL buffer");
     DL4S_REQUIRE(B >= 1 && Sq >= 1 && Sk >= 1 && D >= 1 && Hl >= 1 && dk >= 1 && dv >= 1, "bad extents");
     DL4S_REQUIRE(!causal || Sq == Sk, "the causal mask of DL4S is square: Sq must equal Sk");
-    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16, "unknown precision %d", precision);
+    DL4S_REQUIRE(prec_known(precision), "unknown precision %d", precision);
     MaskSpec mask = make_mask(d_key_lengths, causal, nullptr, nullptr);
-    const bool fused_tc = precision == DL4S_PREC_F16 && d_xq == d_xk && d_xk == d_xv && tc_block_supported(B, Sq, Sk, D, Hl, dk, dv, 0);
+    const bool fused_tc = prec_tc(precision) && d_xq == d_xk && d_xk == d_xv && tc_block_supported(B, Sq, Sk, D, Hl, dk, dv, 0);
     if (fused_tc) {
         ScopedTimer timer(st);
-        return mha_heads_self_tc(st, d_xq, B, Sq, D, Hl, dk, dv, d_wq, d_wk, d_wv, mask, d_heads_out, half_output != 0);
+        return mha_heads_self_tc(st, d_xq, B, Sq, D, Hl, dk, dv, d_wq, d_wk, d_wv, mask, d_heads_out, half_output != 0,
+                                 prec_split(precision));
     }
     if (half_output)
         return fail(DL4S_ERR_UNSUPPORTED, "half output needs the fused tensor-core path (see dl4s_cuda_mha_heads_half_supported)");
     MhaShape s{B, Sq, Sk, D, Hl, dk, dv};
     size_t main_bytes = align_up(mha_heads_scratch_floats(s) * sizeof(float), 1024);
-    size_t extra = precision == DL4S_PREC_F16 ? tc_layer_scratch_bytes(B, Sq > Sk ? Sq : Sk, D, Hl, dk, dv, 0) : 0;
+    size_t extra = prec_tc(precision) ? tc_layer_scratch_bytes(B, Sq > Sk ? Sq : Sk, D, Hl, dk, dv, 0, prec_split(precision)) : 0;
     void *base = nullptr;
     DL4S_TRY(arena_reserve(st, main_bytes + extra, &base));
     ScopedTimer timer(st);
@@ -383,23 +394,23 @@ dl4s_status dl4s_cuda_mha_output_forward(const void *d_heads, const float *d_res
     DL4S_STATE(st);
     DL4S_REQUIRE(d_heads && d_residual && d_wo && d_ln_scale && d_ln_shift && d_out, "NULL buffer");
     DL4S_REQUIRE(B >= 1 && Sq >= 1 && D >= 1 && HDv >= 1, "bad extents");
-    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16, "unknown precision %d", precision);
+    DL4S_REQUIRE(prec_known(precision), "unknown precision %d", precision);
     DL4S_REQUIRE(groups >= 1 && HDv % groups == 0, "%lld column groups do not divide %lld head columns", (long long)groups,
                  (long long)HDv);
     const int64_t C = HDv / groups, M = B * Sq;
     if (groups == 1) group_stride = M * C;
     DL4S_REQUIRE(group_stride >= M * C, "group stride %lld is smaller than one group (%lld elements)", (long long)group_stride,
                  (long long)(M * C));
-    if (precision == DL4S_PREC_F16 && gemm_tc_supported(M, D, HDv) && D % 4 == 0 && C % 64 == 0 && group_stride % 8 == 0) {
+    if (prec_tc(precision) && gemm_tc_supported(M, D, HDv) && D % 4 == 0 && C % 64 == 0 && group_stride % 8 == 0) {
         ScopedTimer timer(st);
         return mha_output_tc(st, d_heads, half_input != 0, d_residual, B, Sq, D, HDv, d_wo, d_ln_scale, d_ln_shift, d_out,
-                             groups, group_stride);
+                             groups, group_stride, prec_split(precision));
     }
     if (half_input)
         return fail(DL4S_ERR_UNSUPPORTED, "half input needs the tensor-core path (see dl4s_cuda_mha_heads_half_supported)");
     size_t main_bytes = align_up((size_t)(M * D) * sizeof(float), 1024);
     size_t rows_bytes = groups > 1 ? align_up((size_t)(M * HDv) * sizeof(float), 1024) : 0;
-    size_t extra = precision == DL4S_PREC_F16 && gemm_tc_supported(M, D, HDv) ? gemm_tc_scratch_bytes(M, D, HDv) : 0;
+    size_t extra = prec_tc(precision) && gemm_tc_supported(M, D, HDv) ? gemm_tc_scratch_bytes(M, D, HDv, prec_split(precision)) : 0;
     void *base = nullptr;
     DL4S_TRY(arena_reserve(st, main_bytes + rows_bytes + extra, &base));
     ScopedTimer timer(st);
@@ -423,13 +434,13 @@ dl4s_status dl4s_cuda_ffn_forward(const float *d_x, int64_t M, int64_t D, int64_
     DL4S_REQUIRE(d_x && d_w1 && d_b1 && d_w2 && d_b2 && d_ln_scale && d_ln_shift && d_out, "NULL buffer");
     DL4S_REQUIRE(M >= 1 && D >= 1 && F >= 1, "bad extents");
     DL4S_REQUIRE(act == DL4S_ACT_GELU_SIGMOID || act == DL4S_ACT_RELU, "unknown activation %d", act);
-    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16, "unknown precision %d", precision);
-    if (precision == DL4S_PREC_F16 && gemm_tc_supported(M, F, D) && gemm_tc_supported(M, D, F) && D % 4 == 0) {
+    DL4S_REQUIRE(prec_known(precision), "unknown precision %d", precision);
+    if (prec_tc(precision) && gemm_tc_supported(M, F, D) && gemm_tc_supported(M, D, F) && D % 4 == 0) {
         ScopedTimer timer(st);
-        return ffn_tc(st, d_x, M, D, F, d_w1, d_b1, d_w2, d_b2, d_ln_scale, d_ln_shift, act, d_out);
+        return ffn_tc(st, d_x, M, D, F, d_w1, d_b1, d_w2, d_b2, d_ln_scale, d_ln_shift, act, d_out, prec_split(precision));
     }
     size_t main_bytes = align_up(ffn_scratch_floats(M, D, F) * sizeof(float), 1024);
-    size_t extra = precision == DL4S_PREC_F16 ? tc_layer_scratch_bytes(1, M, D, 1, 1, 1, F) : 0;
+    size_t extra = prec_tc(precision) ? tc_layer_scratch_bytes(1, M, D, 1, 1, 1, F, prec_split(precision)) : 0;
     void *base = nullptr;
     DL4S_TRY(arena_reserve(st, main_bytes + extra, &base));
     ScopedTimer timer(st);
@@ -445,16 +456,17 @@ dl4s_status dl4s_cuda_encoder_forward(const float *d_x, int64_t B, int64_t S, in
     DL4S_REQUIRE(d_x && d_params && d_out, "NULL buffer");
     DL4S_REQUIRE(B >= 1 && S >= 1 && D >= 1 && H >= 1 && dk >= 1 && dv >= 1 && F >= 1 && layers >= 0, "bad extents");
     DL4S_REQUIRE(act == DL4S_ACT_GELU_SIGMOID || act == DL4S_ACT_RELU, "unknown activation %d", act);
-    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16, "unknown precision %d", precision);
-    if (precision == DL4S_PREC_F16 && layers > 0 && tc_block_supported(B, S, S, D, H, dk, dv, F)) {
+    DL4S_REQUIRE(prec_known(precision), "unknown precision %d", precision);
+    if (prec_tc(precision) && layers > 0 && tc_block_supported(B, S, S, D, H, dk, dv, F)) {
         ScopedTimer timer(st);
-        return encoder_tc(st, d_x, B, S, D, H, dk, dv, F, layers, d_params, make_mask(d_lengths, 0, nullptr, nullptr), act, d_out);
+        return encoder_tc(st, d_x, B, S, D, H, dk, dv, F, layers, d_params, make_mask(d_lengths, 0, nullptr, nullptr), act, d_out,
+                          prec_split(precision));
     }
     MhaShape s{B, S, S, D, H, dk, dv};
     size_t mf = mha_scratch_floats(s), ff = ffn_scratch_floats(B * S, D, F);
     size_t main_floats = (mf > ff ? mf : ff) + 2 * (size_t)(B * S * D);
     size_t main_bytes = align_up(main_floats * sizeof(float), 1024);
-    size_t extra = precision == DL4S_PREC_F16 ? tc_layer_scratch_bytes(B, S, D, H, dk, dv, F) : 0;
+    size_t extra = prec_tc(precision) ? tc_layer_scratch_bytes(B, S, D, H, dk, dv, F, prec_split(precision)) : 0;
     void *base = nullptr;
     DL4S_TRY(arena_reserve(st, main_bytes + extra, &base));
     ScopedTimer timer(st);
@@ -469,7 +481,9 @@ dl4s_status dl4s_cuda_encoder_forward(const float *d_x, int64_t B, int64_t S, in
     }
     const float *cur = d_x;
     const float *p = d_params;
+    ScopedGroup group(st, "Encoder");
     for (int64_t l = 0; l < layers; ++l) {
+        ScopedGroup layer(st, "EncoderLayer");
         const float *wq = p; p += D * H * dk;
         const float *wk = p; p += D * H * dk;
         const float *wv = p; p += D * H * dv;
@@ -490,6 +504,40 @@ dl4s_status dl4s_cuda_encoder_forward(const float *d_x, int64_t B, int64_t S, in
     return DL4S_OK;
 }
 
+dl4s_status dl4s_cuda_encoder_prepare(int64_t D, int64_t H, int64_t dk, int64_t dv, int64_t F, int64_t layers,
+                                      const float *d_params, int32_t precision, void **prepared)
+{
+    DL4S_STATE(st);
+    DL4S_REQUIRE(d_params && prepared, "NULL argument");
+    *prepared = nullptr;
+    DL4S_REQUIRE(D >= 1 && H >= 1 && dk >= 1 && dv >= 1 && F >= 1 && layers >= 1, "bad extents");
+    DL4S_REQUIRE(prec_tc(precision), "weights are prepared for the tensor-core precisions only (got %d)", precision);
+    return encoder_prepare(st, D, H, dk, dv, F, layers, d_params, prec_split(precision), prepared);
+}
+
+dl4s_status dl4s_cuda_encoder_prepared_refresh(void *prepared)
+{
+    DL4S_STATE(st);
+    return encoder_prepared_refresh(st, prepared);
+}
+
+dl4s_status dl4s_cuda_encoder_prepared_destroy(void *prepared)
+{
+    DL4S_STATE(st);
+    return encoder_prepared_destroy(st, prepared);
+}
+
+dl4s_status dl4s_cuda_encoder_forward_prepared(void *prepared, const float *d_x, int64_t B, int64_t S, const int32_t *d_lengths,
+                                               int32_t act, float *d_out)
+{
+    DL4S_STATE(st);
+    DL4S_REQUIRE(prepared && d_x && d_out, "NULL argument");
+    DL4S_REQUIRE(B >= 1 && S >= 1, "bad extents");
+    DL4S_REQUIRE(act == DL4S_ACT_GELU_SIGMOID || act == DL4S_ACT_RELU, "unknown activation %d", act);
+    ScopedTimer timer(st);
+    return encoder_tc_prepared(st, prepared, d_x, B, S, make_mask(d_lengths, 0, nullptr, nullptr), act, d_out);
+}
+
 dl4s_status dl4s_cuda_embed_positional(const int32_t *d_ids, int64_t B, int64_t S, int64_t D, const float *d_embedding,
                                        int64_t vocab, int32_t ignore_index, float *d_out)
 {
@@ -503,7 +551,7 @@ dl4s_status dl4s_cuda_embed_positional(const int32_t *d_ids, int64_t B, int64_t 
             return fail(DL4S_ERR_UNSUPPORTED, "the positional-encoding table has to be built: run the call once before capturing");
         // (re)build the table; the old one may still be in use by work queued on the stream
         DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
-        if (st->pe_table) DL4S_CUDA_TRY(cudaFree(st->pe_table));
+        DL4S_TRY(release_internal(st, st->pe_table));
         st->pe_table = nullptr;
         st->pe_rows = 0;
         DL4S_CUDA_TRY(cudaMalloc((void **)&st->pe_table, (size_t)(S * D) * sizeof(float)));
@@ -513,6 +561,7 @@ dl4s_status dl4s_cuda_embed_positional(const int32_t *d_ids, int64_t B, int64_t 
         k_positional_table<<<(unsigned)tb, 256, 0, st->stream>>>(S, D, st->pe_table);
         DL4S_TRY(after_launch(st, "k_positional_table"));
     }
+    ScopedGroup group(st, "Embedding");
     int64_t blocks = B * S < (int64_t)st->sm_count * 16 ? B * S : (int64_t)st->sm_count * 16;
     k_embed_positional<<<(unsigned)blocks, 256, 0, st->stream>>>(d_ids, B * S, S, D, d_embedding, vocab, ignore_index,
                                                                 sqrtf((float)D), st->pe_table, d_out);

@@ -356,7 +356,7 @@ static dl4s_status launch_gemm_skinny(DeviceState *st, const float *a, const flo
             return fail(DL4S_ERR_UNSUPPORTED, "the split-K buffer would have to grow while a graph is being captured: run the "
                         "same calls once before dl4s_cuda_graph_begin");
         DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
-        if (st->skinny_partials) DL4S_CUDA_TRY(cudaFree(st->skinny_partials));
+        DL4S_TRY(release_internal(st, st->skinny_partials));
         st->skinny_partials = nullptr;
         st->skinny_bytes = 0;
         DL4S_CUDA_TRY(cudaMalloc((void **)&st->skinny_partials, need));

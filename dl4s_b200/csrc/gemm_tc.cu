@@ -66,7 +66,7 @@ __device__ __forceinline__ float gelu_sigmoid_tc(float t)
 }
 
 // fp32 -> half, 8 elements per thread per step.
-__global__ void __launch_bounds__(256) k_f32_to_f16(const float *__restrict__ x, __half *__restrict__ y, int64_t n)
+__global__ void __launch_bounds__(256) k_f32_to_f16(const float *__restrict__ x, __half *__restrict__ y, int64_t n, int32_t *status)
 {
     pdl_launch_dependents();
     pdl_wait();
@@ -75,6 +75,7 @@ __global__ void __launch_bounds__(256) k_f32_to_f16(const float *__restrict__ x,
     int64_t n8 = n >> 3;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
     uint4 *y8 = reinterpret_cast<uint4 *>(y);
+    bool bad = false;   // a value outside the half range
     for (int64_t i = tid; i < n8; i += stride) {
         float4 a = x4[2 * i], b = x4[2 * i + 1];
         __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
@@ -84,9 +85,54 @@ __global__ void __launch_bounds__(256) k_f32_to_f16(const float *__restrict__ x,
         o.y = *reinterpret_cast<uint32_t *>(&h1);
         o.z = *reinterpret_cast<uint32_t *>(&h2);
         o.w = *reinterpret_cast<uint32_t *>(&h3);
+        bad |= half2_not_finite(o.x) | half2_not_finite(o.y) | half2_not_finite(o.z) | half2_not_finite(o.w);
         y8[i] = o;
     }
-    for (int64_t i = (n8 << 3) + tid; i < n; i += stride) y[i] = __float2half_rn(x[i]);
+    for (int64_t i = (n8 << 3) + tid; i < n; i += stride) {
+        const __half hv = __float2half_rn(x[i]);
+        bad |= half2_not_finite((uint32_t)__half_as_ushort(hv));
+        y[i] = hv;
+    }
+    if (bad) atomicOr(status, kStatusHalfRange);
+}
+
+// fp32 -> two halves: hi = half(x), lo = half(x - hi), so that hi + lo carries 22 significant bits of x.
+__global__ void __launch_bounds__(256) k_f32_to_f16_hilo(const float *__restrict__ x, __half *__restrict__ hi, __half *__restrict__ lo,
+                                                         int64_t n, int32_t *status)
+{
+    pdl_launch_dependents();
+    pdl_wait();
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    int64_t n4 = n >> 2;
+    bool bad = false;
+    for (int64_t i = tid; i < n4; i += stride) {
+        const float4 v = reinterpret_cast<const float4 *>(x)[i];
+        uint2 ph, pl;
+        split_hilo(v, ph, pl);
+        bad |= half2_not_finite(ph.x) | half2_not_finite(ph.y);
+        reinterpret_cast<uint2 *>(hi)[i] = ph;
+        reinterpret_cast<uint2 *>(lo)[i] = pl;
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += stride) {
+        const __half h = __float2half_rn(x[i]);
+        bad |= half2_not_finite((uint32_t)__half_as_ushort(h));
+        hi[i] = h;
+        lo[i] = __float2half_rn(x[i] - __half2float(h));
+    }
+    if (bad) atomicOr(status, kStatusHalfRange);
+}
+
+dl4s_status launch_f32_to_f16_hilo(DeviceState *st, const float *x, void *hi, void *lo, int64_t n)
+{
+    if (n == 0) return DL4S_OK;
+    DL4S_REQUIRE((((uintptr_t)x | (uintptr_t)hi | (uintptr_t)lo) & 15) == 0, "conversion buffers must be 16-byte aligned");
+    int64_t blocks = ceil_div(n, 256 * 4 * 4);
+    int64_t cap = (int64_t)st->sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    DL4S_CUDA_TRY(launch_pdl(st, k_f32_to_f16_hilo, dim3((unsigned)blocks), dim3(256), 0, 1, x, (__half *)hi, (__half *)lo, n, st->status_word));
+    return after_launch(st, "k_f32_to_f16_hilo");
 }
 
 dl4s_status launch_f32_to_f16(DeviceState *st, const float *x, void *y, int64_t n)
@@ -97,7 +143,7 @@ dl4s_status launch_f32_to_f16(DeviceState *st, const float *x, void *y, int64_t 
     int64_t cap = (int64_t)st->sm_count * 8;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
-    DL4S_CUDA_TRY(launch_pdl(st, k_f32_to_f16, dim3((unsigned)blocks), dim3(256), 0, 1, x, (__half *)y, n));
+    DL4S_CUDA_TRY(launch_pdl(st, k_f32_to_f16, dim3((unsigned)blocks), dim3(256), 0, 1, x, (__half *)y, n, st->status_word));
     return after_launch(st, "k_f32_to_f16");
 }
 
@@ -112,6 +158,9 @@ struct GemmTcParams {
     double *ln_stats;        // EPI_RESIDUAL_STATS: partial sums per (32 rows, half tile), see tc.cuh
     int32_t *tile_counter;   // {tiles handed out beyond the first gridDim.x, CTAs done}
     int a_kc;                // A's k extent per column group (K when A is one plain matrix)
+    int test_skip_kb;        // -1; test only: the k-block of a CTA's first tile whose loads are left out
+    uint32_t wait_polls;     // poll limit of every bounded wait (kWaitPolls; short under an injected fault)
+    int a_groups;            // column groups of A; the k walk wraps to group 0 after the last one (split B: K = 2 x A's width)
     // OUT_HEADS_F16: columns [part_begin[p], part_begin[p+1]) go to part_ptr[p], a half tensor
     // [B, H, S, part_d[p]] (row m = b*S + s), multiplied by part_scale[p].
     __half *part_ptr[3];
@@ -213,7 +262,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
             const int workers = (int)(gridDim.x / CTAS);
             auto publish = [&](int idx, int t) -> bool {
                 const int s = idx % G_TILE_RING;
-                if (!mbar_wait(&tile_empty[s], ((idx / G_TILE_RING) & 1) ^ 1, abort_flag)) return false;
+                if (!mbar_wait(&tile_empty[s], ((idx / G_TILE_RING) & 1) ^ 1, abort_flag, p.wait_polls)) return false;
                 tile_ring[s] = t;
                 mbar_arrive(&tile_full[s]);
                 if (PAIR) {   // the same slot of the other CTA's ring
@@ -238,7 +287,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                     cur = nxt;
                     nxt = nxt2;
                 } else {
-                    if (!mbar_wait_cluster(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag)) break;
+                    if (!mbar_wait_cluster(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
                     this_tile = tile_ring[slot];
                     mbar_arrive_remote(&tile_empty[slot], 0);
                     if (this_tile >= num_tiles) break;
@@ -248,9 +297,12 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                 const int row0 = (tm * CTAS + (int)rank) * GM, col0 = tn * BN + (int)rank * BN_CTA;
                 int kx = 0, kz = 0;   // A is [groups][rows][a_kc]: k = kz * a_kc + kx
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.wait_polls)) { ok = false; break; }
                     uint8_t *sa = smem + stage * STAGE_BYTES;
-                    if (PAIR) {
+                    if (!PAIR && it == 0 && kb == p.test_skip_kb) {
+                        // Injected fault (dl4s_cuda_inject_failure): this stage is never filled, so the MMA thread's
+                        // bounded wait on it runs out and the CTA unwinds through the common exit.
+                    } else if (PAIR) {
                         // both CTAs' bytes are counted on the leader's barrier
                         if (leader) mbar_expect_tx(&full_bar[stage], STAGE_BYTES * CTAS);
                         tma_load_3d_pair(sa, &tmap_a, &full_bar[stage], kx, row0, kz);
@@ -266,7 +318,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                     }
                     if (++stage == G_STAGES) { stage = 0; phase ^= 1; }
                     kx += GK;
-                    if (kx == p.a_kc) { kx = 0; ++kz; }
+                    if (kx == p.a_kc) { kx = 0; if (++kz == p.a_groups) kz = 0; }
                 }
             }
         }
@@ -276,15 +328,15 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
             bool ok = true;
             for (int it = 0; ok; ++it) {
                 const int slot = it % G_TILE_RING;
-                if (!mbar_wait(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag)) break;
+                if (!mbar_wait(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
                 const int tile = tile_ring[slot];
                 mbar_arrive(&tile_empty[slot]);
                 if (tile >= num_tiles) break;
-                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.wait_polls)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
                 for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.wait_polls)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
                     const uint32_t sb = sa + A_BYTES;
@@ -313,9 +365,9 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
         for (int it = 0; ok; ++it) {
             const int slot = it % G_TILE_RING;
             if (PAIR && !leader) {
-                if (!mbar_wait_cluster(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag)) break;
+                if (!mbar_wait_cluster(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
             } else {
-                if (!mbar_wait(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag)) break;
+                if (!mbar_wait(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
             }
             const int tile = tile_ring[slot];
             __syncwarp();
@@ -326,7 +378,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
             if (tile >= num_tiles) break;
             int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-            if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag)) { ok = false; break; }
+            if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.wait_polls)) { ok = false; break; }
             tc_fence_after();
             // Each warp drains its 32 accumulator rows 32 columns at a time with two 16-lane x 256-bit
             // tensor-memory loads: thread `lane` then holds, for rows lane/4 + {0, 8, 16, 24} of the warp's
@@ -349,6 +401,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                 my_ss = (int)(my_row - (uint32_t)my_bb * (uint32_t)p.S);
             }
             float stat1 = 0.f, stat2 = 0.f;   // EPI_RESIDUAL_STATS: this lane's share of the warp's block
+            bool half_overflow = false;       // half outputs: a result outside the half range
             constexpr bool kHasResidual = (EPI == EPI_BIAS_RESIDUAL || EPI == EPI_RESIDUAL || EPI == EPI_RESIDUAL_STATS);
             // Head-major output, common case: the warp's 32 rows lie in one batch element, so the rows a lane
             // stores (rsub, rsub + 8, ...) are part_d * 8 elements apart and one address per group is enough.
@@ -463,6 +516,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                         } else {
                             __half2 h = __floats2half2_rn(t.x * scale, t.y * scale);
                             h2[pp] = *reinterpret_cast<uint32_t *>(&h);
+                            half_overflow |= half2_not_finite(h2[pp]);
                         }
                     }
                     if (OUT != OUT_F32) {
@@ -509,6 +563,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                     p.ln_stats[2 * slot + 1] = d2;
                 }
             }
+            if (OUT != OUT_F32 && half_overflow) atomicOr(p.status, kStatusHalfRange);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -523,7 +578,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
     tc_fence_before();
     __syncthreads();
     if (threadIdx.x == 0) {
-        if (abort_s) atomicOr(p.status, 0x100);
+        if (abort_s) atomicOr(p.status, kStatusGemmTimeout);
         // This CTA takes no more tiles. The last CTA to get here leaves the counters at zero for the
         // next launch that uses the slot.
         __threadfence();
@@ -590,9 +645,9 @@ bool gemm_tc_supported(int64_t M, int64_t N, int64_t K)
     return M >= GM && N >= 64 && N % 64 == 0 && K >= GK && K % GK == 0 && M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31);
 }
 
-size_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int64_t K)
+size_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int split)
 {
-    return align_up((size_t)(M * K) * 2, 1024) + align_up((size_t)(K * N) * 2, 1024);
+    return align_up((size_t)(M * K) * 2, 1024) + align_up((size_t)(K * N) * (split ? 4 : 2), 1024);
 }
 
 // DL4S_GEMM_PAIRS=0 in the environment selects the single-CTA kernel everywhere (for comparisons).
@@ -635,6 +690,12 @@ static dl4s_status run_gemm_tc_inst2(DeviceState *st, const CUtensorMap &ta, con
     const int grid = (p.tiles_m * p.tiles_n < workers ? p.tiles_m * p.tiles_n : workers) * CTAS;
     p.tile_counter = st->tile_counters + 2 * st->tile_counter_next;
     st->tile_counter_next = (st->tile_counter_next + 1) % kTileCounterSlots;
+    p.test_skip_kb = -1;
+    p.wait_polls = kWaitPolls;
+    if (!PAIR && !st->capturing && take_injected_failure(DL4S_INJECT_WAIT_TIMEOUT)) {
+        p.test_skip_kb = p.K / GK > 1 ? 1 : 0;
+        p.wait_polls = 1u << 16;
+    }
     DL4S_CUDA_TRY(launch_pdl(st, k_gemm_tc<BN, EPI, OUT, PAIR>, dim3((unsigned)grid), dim3(gemm_threads(EPI, PAIR)), smem, CTAS, ta, tb, p));
     return after_launch(st, name);
 }
@@ -680,9 +741,10 @@ static dl4s_status run_gemm_tc(DeviceState *st, const CUtensorMap &ta, const CUt
 
 dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_half, int64_t M, int64_t N, int64_t K,
                              int epilogue, const float *bias, const float *residual, const GemmTcOut &out,
-                             int64_t a_groups, int64_t a_group_stride)
+                             int64_t a_groups, int64_t a_group_stride, int b_split)
 {
     DL4S_REQUIRE(gemm_tc_supported(M, N, K), "shape not supported by the tensor-core gemm");
+    DL4S_REQUIRE(2 * K < (1ll << 31), "K too large");
     DL4S_REQUIRE(!residual || ((uintptr_t)residual & 15) == 0, "residual must be 16-byte aligned");
     DL4S_REQUIRE(a_groups >= 1 && K % a_groups == 0 && (K / a_groups) % GK == 0,
                  "A's column groups must each hold a multiple of %d columns", GK);
@@ -693,11 +755,15 @@ dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_
     // A as [groups][M][kc]: rows past M read as zeros, whatever lies behind them in memory.
     DL4S_TRY(make_tmap_f16(&ta, a_half, (uint64_t)kc, (uint64_t)M, (uint64_t)a_groups, (uint64_t)kc * 2,
                            (uint64_t)a_group_stride * 2, GK, GM));
-    DL4S_TRY(make_tmap_f16(&tb, b_half, (uint64_t)N, (uint64_t)K, 0, (uint64_t)N * 2, 0, 64, GK));
+    // Split B: [W_hi; W_lo] stacked along k. The main loop runs over 2K rows of B while A's k walk wraps after K,
+    // so the accumulator receives A W_hi + A W_lo.
+    const int64_t Kb = b_split ? 2 * K : K;
+    DL4S_TRY(make_tmap_f16(&tb, b_half, (uint64_t)N, (uint64_t)Kb, 0, (uint64_t)N * 2, 0, 64, GK));
     GemmTcParams p;
     p.c = out.c; p.bias = bias; p.residual = residual;
-    p.M = M; p.N = N; p.K = K;
+    p.M = M; p.N = N; p.K = Kb;
     p.a_kc = (int)kc;
+    p.a_groups = (int)a_groups;
     p.ln_stats = out.ln_stats;
     DL4S_REQUIRE(epilogue != EPI_RESIDUAL_STATS || (out.ln_stats && out.mode == OUT_F32), "the statistics epilogue needs its buffer");
     p.epilogue = epilogue;
@@ -732,18 +798,20 @@ dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_
 }
 
 dl4s_status launch_gemm_tc(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K,
-                           int epilogue, const float *bias, const float *residual, void *scratch, size_t scratch_bytes)
+                           int epilogue, const float *bias, const float *residual, void *scratch, size_t scratch_bytes, int split)
 {
     DL4S_REQUIRE(gemm_tc_supported(M, N, K), "shape not supported by the tensor-core gemm");
-    DL4S_REQUIRE(scratch && scratch_bytes >= gemm_tc_scratch_bytes(M, N, K), "scratch too small");
+    DL4S_REQUIRE(scratch && scratch_bytes >= gemm_tc_scratch_bytes(M, N, K, split), "scratch too small");
     __half *ah = (__half *)scratch;
     __half *bh = (__half *)((char *)scratch + align_up((size_t)(M * K) * 2, 1024));
     DL4S_TRY(launch_f32_to_f16(st, a, ah, M * K));
-    DL4S_TRY(launch_f32_to_f16(st, b, bh, K * N));
+    // the second operand is the weight matrix in every caller: it is the one that may enter as two halves
+    if (split) DL4S_TRY(launch_f32_to_f16_hilo(st, b, bh, bh + K * N, K * N));
+    else DL4S_TRY(launch_f32_to_f16(st, b, bh, K * N));
     GemmTcOut out;
     out.mode = OUT_F32;
     out.c = c;
-    return launch_gemm_tc_h(st, ah, bh, M, N, K, epilogue, bias, residual, out);
+    return launch_gemm_tc_h(st, ah, bh, M, N, K, epilogue, bias, residual, out, 1, 0, split);
 }
 
 }  // namespace dl4s

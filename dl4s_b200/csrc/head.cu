@@ -94,7 +94,9 @@ dl4s_status launch_log_softmax_rows(DeviceState *st, const float *x, int64_t row
 }
 
 // E [V, D] fp32 -> E^T [D, V] half: the [K, N] operand layout of the tensor-core GEMM.
-__global__ void __launch_bounds__(256) k_transpose_to_f16(const float *__restrict__ e, int64_t V, int64_t D, __half *__restrict__ et)
+// lo != nullptr: the half-rounded remainders go there (the two-half form of a weight matrix).
+__global__ void __launch_bounds__(256) k_transpose_to_f16(const float *__restrict__ e, int64_t V, int64_t D, __half *__restrict__ et,
+                                                          __half *__restrict__ lo)
 {
     __shared__ float tile[32][33];
     const int64_t v0 = (int64_t)blockIdx.x * 32, d0 = (int64_t)blockIdx.y * 32;
@@ -106,7 +108,12 @@ __global__ void __launch_bounds__(256) k_transpose_to_f16(const float *__restric
     __syncthreads();
     for (int j = ty; j < 32; j += 8) {
         const int64_t d = d0 + j, v = v0 + tx;
-        if (d < D && v < V) et[d * V + v] = __float2half_rn(tile[tx][j]);
+        if (d < D && v < V) {
+            const float w = tile[tx][j];
+            const __half h = __float2half_rn(w);
+            et[d * V + v] = h;
+            if (lo) lo[d * V + v] = __float2half_rn(w - __half2float(h));
+        }
     }
 }
 
@@ -129,24 +136,26 @@ dl4s_status dl4s_cuda_output_head(const float *d_x, int64_t M, int64_t D, const 
     DL4S_STATE(st);
     DL4S_REQUIRE(d_x && d_embedding && d_out, "NULL buffer");
     DL4S_REQUIRE(M >= 1 && D >= 1 && V >= 1, "bad extents");
-    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16, "unknown precision %d", precision);
+    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16 || precision == DL4S_PREC_F16_SPLIT,
+                 "unknown precision %d", precision);
     ScopedTimer timer(st);
     const int epi = d_bias ? EPI_BIAS : EPI_NONE;
-    if (precision == DL4S_PREC_F16 && gemm_tc_supported(M, V, D) && V <= 65535 * 32 &&
+    const int split = precision == DL4S_PREC_F16_SPLIT ? 1 : 0;   // the embedding is the weight operand
+    if (precision != DL4S_PREC_FP32 && gemm_tc_supported(M, V, D) && V <= 65535 * 32 &&
         (((uintptr_t)d_x | (uintptr_t)d_out) & 15) == 0) {
         // x and E^T as half operands, fp32 logits
-        const size_t xb = align_up((size_t)(M * D) * 2, 1024), eb = align_up((size_t)(D * V) * 2, 1024);
+        const size_t xb = align_up((size_t)(M * D) * 2, 1024), eb = align_up((size_t)(D * V) * (split ? 4 : 2), 1024);
         void *base = nullptr;
         DL4S_TRY(arena_reserve(st, xb + eb, &base));
         void *xh = base, *eth = (char *)base + xb;
         DL4S_TRY(launch_f32_to_f16(st, d_x, xh, M * D));
         dim3 grid((unsigned)ceil_div(V, 32), (unsigned)ceil_div(D, 32));
-        k_transpose_to_f16<<<grid, 256, 0, st->stream>>>(d_embedding, V, D, (__half *)eth);
+        k_transpose_to_f16<<<grid, 256, 0, st->stream>>>(d_embedding, V, D, (__half *)eth, split ? (__half *)eth + D * V : nullptr);
         DL4S_TRY(after_launch(st, "k_transpose_to_f16"));
         GemmTcOut o;
         o.mode = OUT_F32;
         o.c = d_out;
-        DL4S_TRY(launch_gemm_tc_h(st, xh, eth, M, V, D, epi, d_bias, nullptr, o));
+        DL4S_TRY(launch_gemm_tc_h(st, xh, eth, M, V, D, epi, d_bias, nullptr, o, 1, 0, split));
     } else {
         DL4S_TRY(launch_gemm_f32(st, d_x, d_embedding, d_out, M, V, D, 1.0f, 0.0f, 0, 1, epi, d_bias, nullptr));
     }

@@ -329,6 +329,19 @@ __global__ void __launch_bounds__(kThreads) k_band(const float *__restrict__ x, 
     }
 }
 
+// result[o, j] = stacked[o * row + j] + add[o, j] for the slab of `inner` columns that starts at `stacked`.
+__global__ void __launch_bounds__(kThreads) k_unstack_add(const float *__restrict__ stacked, int64_t row, const float *__restrict__ add,
+                                                          float *__restrict__ y, int64_t outer, int64_t inner)
+{
+    int64_t n = outer * inner;
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < n; i += stride) {
+        int64_t o = i / inner, j = i - o * inner;
+        y[i] = stacked[o * row + j] + add[i];
+    }
+}
+
 }  // namespace dl4s
 
 using namespace dl4s;
@@ -469,6 +482,58 @@ dl4s_status dl4s_cuda_stack(const float *const *d_buffers, const int64_t *shapes
         off += inner;
     }
     return DL4S_OK;
+}
+
+// unstack / unstackAdd (Engine.swift:543,551; CPUEngine.swift:1025-1085): the inverse of stack. Buffer i receives
+// the slab [outer, inner_i] that starts `off` elements into every [total_inner] row of the stacked tensor.
+static dl4s_status unstack_impl(const float *d_stacked, const float *const *d_add, float *const *d_results, const int64_t *shapes,
+                                int32_t n, int32_t dim, int32_t axis)
+{
+    DL4S_STATE(st);
+    DL4S_REQUIRE(d_stacked && d_results && shapes && n >= 1, "bad arguments");
+    DL4S_REQUIRE(dim >= 1 && dim <= kMaxDim && axis >= 0 && axis < dim, "bad axis");
+    int64_t outer = 1, total_inner = 0;
+    for (int d = 0; d < axis; ++d) outer *= shapes[d];
+    for (int i = 0; i < n; ++i) {
+        const int64_t *sh = shapes + (int64_t)i * dim;
+        int64_t inner = 1, o = 1;
+        for (int d = 0; d < axis; ++d) o *= sh[d];
+        DL4S_REQUIRE(o == outer, "leading extents of buffer %d differ", i);
+        for (int d = axis; d < dim; ++d) inner *= sh[d];
+        total_inner += inner;
+    }
+    int64_t off = 0;
+    for (int i = 0; i < n; ++i) {
+        const int64_t *sh = shapes + (int64_t)i * dim;
+        int64_t inner = 1;
+        for (int d = axis; d < dim; ++d) inner *= sh[d];
+        if (inner == 0 || outer == 0) continue;
+        DL4S_REQUIRE(d_results[i] && (!d_add || d_add[i]), "buffer %d is NULL", i);
+        if (d_add) {
+            k_unstack_add<<<grid_for(st, outer * inner, kThreads * 2), kThreads, 0, st->stream>>>(d_stacked + off, total_inner, d_add[i],
+                                                                                               d_results[i], outer, inner);
+            DL4S_TRY(after_launch(st, "k_unstack_add"));
+        } else {
+            DL4S_CUDA_TRY(cudaMemcpy2DAsync(d_results[i], (size_t)inner * sizeof(float), d_stacked + off,
+                                            (size_t)total_inner * sizeof(float), (size_t)inner * sizeof(float), (size_t)outer,
+                                            cudaMemcpyDeviceToDevice, st->stream));
+        }
+        off += inner;
+    }
+    return DL4S_OK;
+}
+
+dl4s_status dl4s_cuda_unstack(const float *d_stacked, float *const *d_results, const int64_t *shapes, int32_t n, int32_t dim,
+                              int32_t axis)
+{
+    return unstack_impl(d_stacked, nullptr, d_results, shapes, n, dim, axis);
+}
+
+dl4s_status dl4s_cuda_unstack_add(const float *d_stacked, const float *const *d_add, float *const *d_results, const int64_t *shapes,
+                                  int32_t n, int32_t dim, int32_t axis)
+{
+    DL4S_REQUIRE(d_add, "add is NULL");
+    return unstack_impl(d_stacked, d_add, d_results, shapes, n, dim, axis);
 }
 
 dl4s_status dl4s_cuda_band(const float *d_src, int64_t rows, int64_t cols, int32_t below, int32_t has_below, int32_t above,

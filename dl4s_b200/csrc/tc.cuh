@@ -9,9 +9,10 @@ namespace dl4s {
 // accumulation in tensor memory. Needs K % 64 == 0 and N % 64 == 0 (TMA boxes
 // of 128 bytes); other shapes use the fp32 kernel.
 bool gemm_tc_supported(int64_t M, int64_t N, int64_t K);
-size_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int64_t K);
+size_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int split = 0);
 dl4s_status launch_gemm_tc(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K,
-                           int epilogue, const float *bias, const float *residual, void *scratch, size_t scratch_bytes);
+                           int epilogue, const float *bias, const float *residual, void *scratch, size_t scratch_bytes,
+                           int split = 0);
 
 // The same product with operands that are already half ([M,K] and [K,N], 16-byte aligned)
 // and a choice of output: fp32 [M,N], half [M,N], or half scattered head-major into up to
@@ -35,12 +36,16 @@ struct GemmTcOut {
 };
 // Number of (sum, sum of squares) pairs EPI_RESIDUAL_STATS leaves per 32 rows for a product with N columns.
 int gemm_tc_stats_per_row_block(int64_t N);
+// b_split != 0: `b_half` is [2K, N], the half-rounded matrix on top of the half-rounded remainder (W_hi; W_lo); the
+// product is A W_hi + A W_lo in one accumulator, i.e. B enters with ~22 significant bits at twice the MMA work.
 // A may be given as `a_groups` column blocks: element (m, g*K/a_groups + c) lies at
 // a_half[g * a_group_stride + m * K/a_groups + c] (the rank-major layout of an all-gather).
 dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_half, int64_t M, int64_t N, int64_t K,
                              int epilogue, const float *bias, const float *residual, const GemmTcOut &out,
-                             int64_t a_groups = 1, int64_t a_group_stride = 0);
+                             int64_t a_groups = 1, int64_t a_group_stride = 0, int b_split = 0);
 dl4s_status launch_f32_to_f16(DeviceState *st, const float *x, void *y, int64_t n);
+// hi = half(x), lo = half(x - hi): the two-half form of a weight matrix (b_split above reads [hi; lo] stacked along k).
+dl4s_status launch_f32_to_f16_hilo(DeviceState *st, const float *x, void *hi, void *lo, int64_t n);
 
 // attn_prefill.cu — flash-style attention with tcgen05 MMAs. Masks are
 // structural only (key lengths and/or causal).
@@ -61,22 +66,30 @@ dl4s_status launch_attn_prefill_tc_h(DeviceState *st, const void *qh, const void
 // encoder_tc.cu — the fused tensor-core pipelines (intermediates in half, no conversion passes).
 // They reserve their own scratch from the device arena.
 bool tc_block_supported(int64_t B, int64_t Sq, int64_t Sk, int64_t D, int64_t H, int64_t dk, int64_t dv, int64_t F);
+// `split` != 0: weights as two halves (hi + lo), see encoder_tc.cu.
 dl4s_status mha_self_tc(DeviceState *st, const float *x, int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk, int64_t dv,
                         const float *wq, const float *wk, const float *wv, const float *wo, const float *g, const float *sh,
-                        const MaskSpec &mask, float *out);
+                        const MaskSpec &mask, float *out, int split);
 dl4s_status mha_heads_self_tc(DeviceState *st, const float *x, int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk,
                               int64_t dv, const float *wq, const float *wk, const float *wv, const MaskSpec &mask, void *out,
-                              int out_half);
+                              int out_half, int split);
 dl4s_status mha_output_tc(DeviceState *st, const void *heads, int heads_half, const float *residual, int64_t B, int64_t S,
                           int64_t D, int64_t HDv, const float *wo, const float *g, const float *sh, float *out,
-                          int64_t groups = 1, int64_t group_stride = 0);
+                          int64_t groups, int64_t group_stride, int split);
 dl4s_status ffn_tc(DeviceState *st, const float *x, int64_t M, int64_t D, int64_t F, const float *w1, const float *b1,
-                   const float *w2, const float *b2, const float *g, const float *sh, int act, float *out);
+                   const float *w2, const float *b2, const float *g, const float *sh, int act, float *out, int split);
 dl4s_status encoder_tc(DeviceState *st, const float *x, int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk, int64_t dv,
-                       int64_t F, int64_t layers, const float *params, const MaskSpec &mask, int act, float *out);
+                       int64_t F, int64_t layers, const float *params, const MaskSpec &mask, int act, float *out, int split);
+// Half weights of a whole encoder converted once and kept in device memory of their own.
+dl4s_status encoder_prepare(DeviceState *st, int64_t D, int64_t H, int64_t dk, int64_t dv, int64_t F, int64_t layers,
+                            const float *params, int split, void **handle);
+dl4s_status encoder_prepared_refresh(DeviceState *st, void *handle);
+dl4s_status encoder_prepared_destroy(DeviceState *st, void *handle);
+dl4s_status encoder_tc_prepared(DeviceState *st, void *handle, const float *x, int64_t B, int64_t S, const MaskSpec &mask, int act,
+                                float *out);
 
 // Scratch one encoder layer's tensor-core kernels need at most (operand copies
 // in half precision); F == 0 leaves the feed-forward GEMMs out.
-size_t tc_layer_scratch_bytes(int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk, int64_t dv, int64_t F);
+size_t tc_layer_scratch_bytes(int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk, int64_t dv, int64_t F, int split = 0);
 
 }  // namespace dl4s

@@ -62,9 +62,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 }
 // Bounded wait. Returns false when it gave up or when another role already
 // raised *abort (a word in shared memory); the caller then leaves its loop.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t polls = kWaitPolls)
 {
-    for (uint32_t i = 0; i < kWaitPolls; ++i) {
+    for (uint32_t i = 0; i < polls; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
     }
@@ -266,9 +266,9 @@ __device__ __forceinline__ void st_remote_u32(void *p, uint32_t cta, uint32_t v)
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(mapa_u32(p, cta)), "r"(v) : "memory");
 }
 // Bounded wait that also orders data another CTA wrote before its arrive.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag)
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t polls = kWaitPolls)
 {
-    for (uint32_t i = 0; i < kWaitPolls; ++i) {
+    for (uint32_t i = 0; i < polls; ++i) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred P;\n\t"

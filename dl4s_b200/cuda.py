@@ -252,7 +252,7 @@ class CUDAMemoryOperators:
         if all(i is None for i in idx[lead:]):
             off = sum(idx[d] * strides[d] for d in range(lead))
             shape = buf.shape[lead:]
-            return ShapedBuffer(buf.ptr + off * 4, shape, buf.dtype, parent=buf.parent or buf), False, shape
+            return ShapedBuffer(buf.ptr + off * buf.dtype.itemsize, shape, buf.dtype, parent=buf.parent or buf), False, shape
         keep = [d for d in range(buf.dim) if idx[d] is None]
         off = sum(idx[d] * strides[d] for d in range(buf.dim) if idx[d] is not None)
         shape = tuple(buf.shape[d] for d in keep)
@@ -419,6 +419,21 @@ class CUDAEngine:
         ptrs = (c_vp * n)(*[b.ptr for b in buffers])
         shapes = _i64arr([s for b in buffers for s in b.shape])
         call("dl4s_cuda_stack", ptrs, shapes, n, dim, axis, c_vp(result.ptr))
+
+    @staticmethod
+    def unstack(stacked, result, axis):
+        """EngineType.unstack (Engine.swift:551): `result` is the list of buffers to fill."""
+        n, dim = len(result), result[0].dim
+        ptrs = (c_vp * n)(*[b.ptr for b in result])
+        call("dl4s_cuda_unstack", c_vp(stacked.ptr), ptrs, _i64arr([s for b in result for s in b.shape]), n, dim, axis)
+
+    @staticmethod
+    def unstackAdd(stacked, add, result, axis):
+        """EngineType.unstackAdd (Engine.swift:543): result[i] = slab i of `stacked` + add[i]."""
+        n, dim = len(result), result[0].dim
+        ptrs = (c_vp * n)(*[b.ptr for b in result])
+        adds = (c_vp * n)(*[b.ptr for b in add])
+        call("dl4s_cuda_unstack_add", c_vp(stacked.ptr), adds, ptrs, _i64arr([s for b in result for s in b.shape]), n, dim, axis)
 
     @staticmethod
     def band(buffer, result, belowDiagonal=None, aboveDiagonal=None):

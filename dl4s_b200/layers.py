@@ -256,6 +256,35 @@ class TransformerEncoder:
         flat = np.concatenate([np.ascontiguousarray(l[k], np.float32).ravel() for l in self.host_layers
                                for k in PARAM_ORDER]) if layerCount else np.zeros(1, np.float32)
         self.params = tensor(flat)
+        self._prepared = {}       # precision -> handle of dl4s_cuda_encoder_prepare
+
+    def prepareWeights(self, precision: Optional[int] = None) -> None:
+        """Convert the weights for the tensor cores once (DL4S keeps parameters as fp32 tensors; the half copies
+        the kernels read do not change between inference calls). Done on the first forward if not called."""
+        prec = CUDAEngine.precision if precision is None else precision
+        if prec == _lib.PREC_FP32 or prec in self._prepared or self.layerCount == 0:
+            return
+        h = c_vp(0)
+        call("dl4s_cuda_encoder_prepare", self.modelDim, self.heads, self.keyDim, self.valueDim, self.forwardDim,
+             self.layerCount, c_vp(self.params.ptr), prec, ctypes.byref(h))
+        self._prepared[prec] = h
+
+    def weightsChanged(self) -> None:
+        """Call after writing new values into `params` (an optimiser step): the prepared copies are converted again."""
+        for h in self._prepared.values():
+            call("dl4s_cuda_encoder_prepared_refresh", h)
+
+    def releasePreparedWeights(self) -> None:
+        for h in self._prepared.values():
+            call("dl4s_cuda_encoder_prepared_destroy", h)
+        self._prepared = {}
+
+    def __del__(self):
+        try:
+            for h in self._prepared.values():
+                _lib.load().dl4s_cuda_encoder_prepared_destroy(h)
+        except Exception:
+            pass
 
     def __call__(self, inputs: ShapedBuffer, sequenceLengths=None, out: Optional[ShapedBuffer] = None) -> ShapedBuffer:
         B, S, D = inputs.shape
@@ -264,6 +293,15 @@ class TransformerEncoder:
         lp = c_vp(mask.lengths.ptr) if mask is not None and mask.lengths is not None else c_vp(0)
         out = out or CUDA.Memory.allocateBuffer((B, S, D))
         prec = CUDAEngine.precision if self.precision is None else self.precision
+        if prec != _lib.PREC_FP32 and self.layerCount > 0:
+            self.prepareWeights(prec)
+            try:
+                call("dl4s_cuda_encoder_forward_prepared", self._prepared[prec], c_vp(inputs.ptr), B, S, lp, self.activation,
+                     c_vp(out.ptr))
+                return out
+            except _lib.DL4SCudaError as e:
+                if e.status != -4:      # DL4S_ERR_UNSUPPORTED: a shape outside the tensor-core pipeline
+                    raise
         call("dl4s_cuda_encoder_forward", c_vp(inputs.ptr), B, S, D, self.heads, self.keyDim, self.valueDim,
              self.forwardDim, self.layerCount, c_vp(self.params.ptr), lp, self.activation, c_vp(out.ptr), prec)
         return out

@@ -18,9 +18,12 @@ a layer that spans G GPUs splits like this:
 With `chunks` > 1 the batch is worked through in chunks, each a complete small layer,
 and the all-gather of chunk c runs on a second stream while chunk c+1 computes.
 
-torch.distributed is the plumbing (process group, the collective); the gathered
-data lies in local HBM before any kernel of this library touches it. The pure
-index helpers below are shared with the CPU (gloo) tests.
+The layer, its NCCL communicator, the second stream and the gather buffers live behind
+the C ABI (dl4s_cuda_comm_* and dl4s_cuda_mha_forward_sharded in include/dl4s_cuda.h);
+this module binds them and needs neither torch nor any other Python package for the
+collective. How the 128-byte communicator id gets from rank 0 to the other ranks is the
+launcher's business (bench.py broadcasts it over its process group, the tests use a
+pipe). The pure index helpers below restate the library's batch split for the CPU tests.
 """
 from __future__ import annotations
 
@@ -90,21 +93,63 @@ def owned_batches(batch: int, world: int, rank: int, chunks: int):
     return idx
 
 
-class HeadShardedMultiHeadAttention:
-    """The layer above on the CUDA device. Construct on every rank with the FULL host weights; each rank uploads
-    only its slices. `__call__(x, mask)` takes the full input [B, S, D] (replicated) and returns this rank's part of
-    the output [len(owned_batches), S, D] as a ShapedBuffer. With chunks > 1 (and more than one rank) the gather of
-    chunk c runs on a second stream under the compute of chunk c+1."""
+def comm_unique_id() -> bytes:
+    """Rank 0: the 128-byte id every rank passes to comm_init."""
+    import ctypes
+    from ._lib import call
+    buf = (ctypes.c_uint8 * 128)()
+    call("dl4s_cuda_comm_unique_id", buf)
+    return bytes(buf)
 
-    def __init__(self, heads: int, hiddenDim: int, keyDim: int, valueDim: int, weights: dict, group=None,
+
+def comm_init(rank: int, world: int, unique_id: Optional[bytes] = None) -> None:
+    """The current device joins the communicator (collective: every rank calls it)."""
+    import ctypes
+    from ._lib import call
+    if world > 1:
+        assert unique_id is not None and len(unique_id) == 128
+        buf = (ctypes.c_uint8 * 128).from_buffer_copy(unique_id)
+        call("dl4s_cuda_comm_init", rank, world, buf)
+    else:
+        call("dl4s_cuda_comm_init", rank, world, None)
+
+
+def comm_destroy() -> None:
+    from ._lib import call
+    call("dl4s_cuda_comm_destroy")
+
+
+def comm_info() -> Tuple[int, int, int]:
+    """(rank, world, NCCL version in use or 0)."""
+    import ctypes
+    from ._lib import call
+    r, w, v = ctypes.c_int32(0), ctypes.c_int32(1), ctypes.c_int32(0)
+    call("dl4s_cuda_comm_info", ctypes.byref(r), ctypes.byref(w), ctypes.byref(v))
+    return r.value, w.value, v.value
+
+
+def comm_timing() -> Tuple[float, float]:
+    """(gather ms, exposed ms) of the last sharded forward on this device; waits for it."""
+    import ctypes
+    from ._lib import call
+    g, e = ctypes.c_float(0), ctypes.c_float(0)
+    call("dl4s_cuda_comm_timing", ctypes.byref(g), ctypes.byref(e))
+    return g.value, e.value
+
+
+class HeadShardedMultiHeadAttention:
+    """The layer above on the CUDA device. Call comm_init on every rank first (a device that never joined runs as a
+    world of one). Construct on every rank with the FULL host weights; each rank uploads only its column slices.
+    `__call__(x, mask)` takes the full input [B, S, D] (replicated on every rank) and returns this rank's part of the
+    output [len(owned_batches), S, D] as a ShapedBuffer. With chunks > 1 (and more than one rank) the gather of
+    chunk c runs on a second stream under the compute of chunk c+1. Every rank must make the same calls in the same
+    order: each call contains collectives."""
+
+    def __init__(self, heads: int, hiddenDim: int, keyDim: int, valueDim: int, weights: dict,
                  precision: Optional[int] = None, chunks: int = 1):
-        import torch
-        import torch.distributed as dist
         from . import cuda
-        self.torch, self.dist, self.cuda = torch, dist, cuda
-        self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.cuda = cuda
+        self.rank, self.world, _ = comm_info()
         self.heads, self.keyDim, self.valueDim, self.hiddenDim = heads, keyDim, valueDim, hiddenDim
         h0, h1 = head_range(heads, self.world, self.rank)
         self.local_heads = h1 - h0
@@ -116,126 +161,30 @@ class HeadShardedMultiHeadAttention:
         self.fc = cuda.tensor(weights["fc"])
         self.norm_scale = cuda.tensor(weights.get("norm_scale", np.ones(hiddenDim, np.float32)))
         self.norm_shift = cuda.tensor(weights.get("norm_shift", np.zeros(hiddenDim, np.float32)))
-        self._bufs = {}
-        self._comm_stream = None
 
     def owned_batches(self, batch: int):
-        return owned_batches(batch, self.world, self.rank, self.chunks)
-
-    def _torch_buffer(self, name, shape, half=False):
-        """Collective buffers are torch tensors (torch.distributed needs them); the library gets their addresses."""
-        dtype = self.torch.float16 if half else self.torch.float32
-        t = self._bufs.get(name)
-        if t is None or tuple(t.shape) != tuple(shape) or t.dtype != dtype:
-            t = self.torch.empty(shape, dtype=dtype, device="cuda")
-            self._bufs[name] = t
-        return t
-
-    def _half_heads(self, prec, plan, S, D):
-        """On the tensor-core path the head outputs only feed the half operand of Wo, so they are produced,
-        gathered and consumed as IEEE half: half the bytes over NVLink, no conversion pass."""
-        import ctypes
-        from ._lib import PREC_F16, call
-        if prec != PREC_F16:
-            return False
-        sizes = set()
-        for c0, c1, lb0, lb1, _o in plan:
-            sizes.add(c1 - c0)
-            if lb1 > lb0:
-                sizes.add(lb1 - lb0)
-        for b in sizes:
-            flag = ctypes.c_int32(0)
-            call("dl4s_cuda_mha_heads_half_supported", b, S, D, self.local_heads, self.keyDim, self.valueDim,
-                 self.heads * self.valueDim, ctypes.byref(flag))
-            if not flag.value:
-                return False
-        return True
-
-    def _streams(self):
-        """(stream the library launches on, second stream for the collective), both as torch streams."""
+        """Global batch indices of the rows of this rank's output, in output order (asked of the library)."""
         import ctypes
         from ._lib import call
-        torch = self.torch
-        ptr = ctypes.c_void_p(0)
-        call("dl4s_cuda_get_stream", ctypes.byref(ptr))
-        cur = torch.cuda.current_stream()
-        main = cur if (ptr.value or 0) == cur.cuda_stream else torch.cuda.ExternalStream(ptr.value or 0)
-        if self._comm_stream is None:
-            self._comm_stream = torch.cuda.Stream()
-        return main, self._comm_stream
+        rows = ctypes.c_int64(0)
+        idx = (ctypes.c_int64 * max(batch, 1))()
+        call("dl4s_cuda_mha_sharded_plan", batch, self.world, self.rank, self.chunks, ctypes.byref(rows), idx)
+        return [int(idx[i]) for i in range(rows.value)]
 
     def __call__(self, x, mask=None, out=None):
         from ._lib import c_vp, call
         from .cuda import CUDAEngine, StructuredMask
-        cuda, torch = self.cuda, self.torch
+        cuda = self.cuda
         B, S, D = x.shape
-        Hl, dk, dv, G = self.local_heads, self.keyDim, self.valueDim, self.world
-        C = Hl * dv
         lens_ptr, causal = 0, 0
         if mask is not None:
             assert isinstance(mask, StructuredMask), "the sharded layer takes structural masks"
             lens_ptr = mask.lengths.ptr if mask.lengths is not None else 0
             causal = int(mask.causal)
         prec = CUDAEngine.precision if self.precision is None else self.precision
-        plan = chunk_plan(B, G, self.rank, self.chunks)
-        half = self._half_heads(prec, plan, S, D)
-        esz = 2 if half else 4
-        bc_max = max(c1 - c0 for c0, c1, *_ in plan)
-        # one rank-major gather buffer [G, Bc, S, C] per chunk; a rank writes its heads straight into its slot
-        gathered = self._torch_buffer("gathered", (len(plan), G * bc_max * S * C), half)
-        rows_out = sum(lb1 - lb0 for _c0, _c1, lb0, lb1, _o in plan)
+        rows_out = len(self.owned_batches(B))
         out = out or cuda.CUDA.Memory.allocateBuffer((rows_out, S, D))
-        overlap = G > 1 and len(plan) > 1
-        main, comm = self._streams() if overlap else (None, None)
-
-        def heads(i):
-            c0, c1, *_ = plan[i]
-            Bc = c1 - c0
-            xp = x.ptr + c0 * S * D * 4
-            slot = gathered[i].data_ptr() + self.rank * Bc * S * C * esz
-            call("dl4s_cuda_mha_heads_forward", c_vp(xp), c_vp(xp), c_vp(xp), Bc, S, S, D, Hl, dk, dv,
-                 c_vp(self.qDense.ptr), c_vp(self.kDense.ptr), c_vp(self.vDense.ptr),
-                 c_vp(lens_ptr + 4 * c0 if lens_ptr else 0), causal, c_vp(slot), prec, int(half))
-
-        def gather(i):
-            """ONE collective per chunk: in-place all-gather of the head outputs (NCCL over NVLink)."""
-            if G == 1:
-                return None
-            c0, c1, *_ = plan[i]
-            n = (c1 - c0) * S * C
-            full = gathered[i][:G * n]
-            mine = full[self.rank * n:(self.rank + 1) * n]
-            if not overlap:
-                self.dist.all_gather_into_tensor(full, mine, group=self.group)
-                return None
-            ready = torch.cuda.Event()
-            ready.record(main)
-            comm.wait_event(ready)
-            with torch.cuda.stream(comm):
-                self.dist.all_gather_into_tensor(full, mine, group=self.group)
-            done = torch.cuda.Event()
-            done.record(comm)
-            return done
-
-        def output(i, done):
-            c0, c1, lb0, lb1, out0 = plan[i]
-            Bc, Bl = c1 - c0, lb1 - lb0
-            if Bl == 0:
-                return
-            if done is not None:
-                main.wait_event(done)
-            hp = gathered[i].data_ptr() + lb0 * S * C * esz
-            call("dl4s_cuda_mha_output_forward", c_vp(hp), c_vp(x.ptr + (c0 + lb0) * S * D * 4), Bl, S, D, G * C,
-                 c_vp(self.fc.ptr), c_vp(self.norm_scale.ptr), c_vp(self.norm_shift.ptr),
-                 c_vp(out.ptr + out0 * S * D * 4), prec, int(half), G, Bc * S * C)
-
-        # Launch order on the compute stream: H0 H1 O0 H2 O1 ... so that gather(i) hides behind H(i+1).
-        pending = None
-        for i in range(len(plan)):
-            heads(i)
-            done = gather(i)
-            if pending is not None:
-                output(*pending)
-            pending = (i, done)
-        output(*pending)
+        call("dl4s_cuda_mha_forward_sharded", c_vp(x.ptr), B, S, D, self.heads, self.keyDim, self.valueDim,
+             c_vp(self.qDense.ptr), c_vp(self.kDense.ptr), c_vp(self.vDense.ptr), c_vp(self.fc.ptr),
+             c_vp(self.norm_scale.ptr), c_vp(self.norm_shift.ptr), c_vp(lens_ptr), causal, c_vp(out.ptr), prec, self.chunks)
         return out

@@ -42,17 +42,30 @@ enum {
     DL4S_ERR_CUDA = -3,
     DL4S_ERR_UNSUPPORTED = -4,
     DL4S_ERR_TIMEOUT = -5, /* a bounded device-side wait gave up; see dl4s_cuda_device_status */
-    DL4S_ERR_NOT_INITIALIZED = -6
+    DL4S_ERR_NOT_INITIALIZED = -6,
+    DL4S_ERR_NCCL = -7     /* the collective library is missing, or a communicator / collective call failed */
 };
 
 /* Arithmetic used by the fused kernels.
- *  DL4S_PREC_FP32 : fp32 FFMA everywhere (check kernels; agrees with the DL4S
- *                   CPU engine to ~1e-5).
- *  DL4S_PREC_F16  : tensor-core path. Operands are rounded to IEEE half
- *                   (11-bit significand, the same as TF32) and multiplied by
- *                   tcgen05 MMAs with fp32 accumulation in tensor memory.
- *                   Inputs must lie within the half range (|x| < 65504). */
-enum { DL4S_PREC_FP32 = 0, DL4S_PREC_F16 = 1 };
+ *  DL4S_PREC_FP32      : fp32 FFMA everywhere (check kernels; agrees with the DL4S
+ *                        CPU engine to ~1e-5).
+ *  DL4S_PREC_F16       : tensor-core path. Operands are rounded to IEEE half
+ *                        (11-bit significand, the same as TF32) and multiplied by
+ *                        tcgen05 MMAs with fp32 accumulation in tensor memory.
+ *  DL4S_PREC_F16_SPLIT : the same path with every weight matrix kept as the sum of
+ *                        two halves (the rounded value and the rounded remainder,
+ *                        ~22 significant bits); the projections and the feed-forward
+ *                        products cost twice the MMA work. Activations and the
+ *                        attention products are as in DL4S_PREC_F16. For stacks of
+ *                        layers whose output must stay within max-abs 2e-3 of the
+ *                        fp32 engine: rounding the weights once is what dominates the
+ *                        error of a deep stack (6-layer encoder, d_model 512: max-abs
+ *                        3e-3 with DL4S_PREC_F16, 1.5e-3 with DL4S_PREC_F16_SPLIT;
+ *                        relative L2 6.7e-4 and 2.9e-4).
+ * On both tensor-core paths operands must lie within the half range (|x| < 65504): a
+ * value that does not sets bit 0x400 of the device status word (dl4s_cuda_device_status
+ * then returns DL4S_ERR_INVALID_ARG); the results of that call are not usable. */
+enum { DL4S_PREC_FP32 = 0, DL4S_PREC_F16 = 1, DL4S_PREC_F16_SPLIT = 2 };
 
 /* Feed-forward activation. 0 is what DL4S computes (PointwiseFeedForward.swift:76). */
 enum { DL4S_ACT_GELU_SIGMOID = 0, DL4S_ACT_RELU = 1 };
@@ -79,7 +92,8 @@ const char *dl4s_cuda_last_error(void);
 int32_t dl4s_cuda_version(void);
 /* Reads and clears the device status word (0 = clean): kernels with bounded waits set bits
  * 0x001-0x100 when a wait runs out (DL4S_ERR_TIMEOUT); a decode step that found its
- * key/value cache full sets 0x200 (DL4S_ERR_INVALID_ARG). Synchronises the stream. */
+ * key/value cache full sets 0x200, a tensor-core operand outside the half range 0x400
+ * (both DL4S_ERR_INVALID_ARG). Synchronises the stream. */
 dl4s_status dl4s_cuda_device_status(int32_t *status_word);
 /* Milliseconds the device spent in the last fused call, measured with CUDA
  * events on the library's stream when timing is enabled (enable != 0). */
@@ -93,6 +107,27 @@ dl4s_status dl4s_cuda_get_timing(float *ms);
  * of a kernel runs from the end of the previous launch to its own end. */
 dl4s_status dl4s_cuda_profile_begin(void);
 dl4s_status dl4s_cuda_profile_end(char *report, size_t capacity);
+/* The reference's operation groups (OperationGroup.capture(named:), Tensor/Graph.swift:134-163: "Encoder",
+ * "EncoderLayer", "MultiHeadAttention", "ScaledDotProductAttention", "PointwiseFeedForward", "LayerNorm", "Dense",
+ * "Embedding") as NVTX ranges around the launches they cover, for a timeline profiler. Off by default; on with
+ * enable != 0 or DL4S_CUDA_TRACE=1 in the environment at dl4s_cuda_init. While on, the group paths entered
+ * ("Encoder/EncoderLayer/MultiHeadAttention", one per line, in order) are also kept on the host (64 KB);
+ * trace_read copies them out and clears the list. */
+dl4s_status dl4s_cuda_set_trace(int32_t enable);
+dl4s_status dl4s_cuda_trace_read(char *report, size_t capacity);
+/* Failure injection for tests of the error path (DL4S itself aborts the process on such failures, e.g.
+ * Engine/CPU/CPU.swift:71-84 has no failure return): the next `count` operations of kind `what` fail with the
+ * status they would report for a real failure and a message that says "injected failure"; count = 0 clears.
+ * Works before dl4s_cuda_init and without a device, so the error plumbing of a binding can be tested anywhere.
+ *  DL4S_INJECT_MALLOC        dl4s_cuda_malloc                      -> DL4S_ERR_OOM
+ *  DL4S_INJECT_H2D           dl4s_cuda_memcpy_h2d / _h2d_async     -> DL4S_ERR_CUDA
+ *  DL4S_INJECT_COMM          dl4s_cuda_comm_init                   -> DL4S_ERR_NCCL
+ *  DL4S_INJECT_WAIT_TIMEOUT  the next single-CTA tensor-core GEMM launch leaves out one operand load and polls
+ *                            with a short limit: its bounded wait runs out, the kernel leaves through its normal
+ *                            exit (nothing traps or hangs) and dl4s_cuda_device_status reports DL4S_ERR_TIMEOUT;
+ *                            the product of that launch is garbage. */
+enum { DL4S_INJECT_MALLOC = 1, DL4S_INJECT_H2D = 2, DL4S_INJECT_COMM = 3, DL4S_INJECT_WAIT_TIMEOUT = 4 };
+dl4s_status dl4s_cuda_inject_failure(int32_t what, int32_t count);
 /* CUDA graphs. Between begin and end the calls made on the current device are RECORDED (stream capture on
  * the library's stream) instead of run; end returns a handle that replays them with one launch. The recorded
  * calls must not allocate, free, wait or read back: buffers are allocated before, and the same calls have run
@@ -180,6 +215,13 @@ dl4s_status dl4s_cuda_permute_axes(const float *d_val, const int64_t *shape, int
 /* stack: concatenates n buffers along `axis`; shapes[i] holds `dim` extents each. */
 dl4s_status dl4s_cuda_stack(const float *const *d_buffers, const int64_t *shapes, int32_t n, int32_t dim,
                             int32_t axis, float *d_result);                                          /* :536 */
+/* unstack: the inverse of stack (the backward of Tensor(stacking:), Tensor/Operators/Stack.swift:79-122): buffer i
+ * of shape shapes[i] receives its slab of the stacked tensor. unstack_add adds d_add[i] to the slab on the way
+ * (gradient accumulation). CPUEngine.swift:1025-1085. */
+dl4s_status dl4s_cuda_unstack(const float *d_stacked, float *const *d_results, const int64_t *shapes, int32_t n,
+                              int32_t dim, int32_t axis);                                            /* :551 */
+dl4s_status dl4s_cuda_unstack_add(const float *d_stacked, const float *const *d_add, float *const *d_results,
+                                  const int64_t *shapes, int32_t n, int32_t dim, int32_t axis);      /* :543 */
 /* band: keeps src[i,j] for i-below <= j <= i+above, zero elsewhere; a negative
  * has_* flag of 0 means "unbounded" (nil in DL4S). CPUEngine.swift:1135-1158. */
 dl4s_status dl4s_cuda_band(const float *d_src, int64_t rows, int64_t cols, int32_t below, int32_t has_below,
@@ -233,8 +275,13 @@ dl4s_status dl4s_cuda_sdpa_decode(const float *d_q, const float *d_k, const floa
  *  - Limit: B*H*ceil(Lmax/chunk)*(d+2) <= 2,097,152 floats for some chunk in
  *    {256, 512, ..., 8192}; larger problems are rejected with
  *    DL4S_ERR_UNSUPPORTED and a message, nothing is launched.
- *  - The first call on each device looks the array's address up
- *    (cudaGetSymbolAddress); make that first call before any stream capture.
+ *  - dl4s_cuda_init looks the array's address up for each device it is given
+ *    (cudaGetSymbolAddress with that device current) and loads the two decode
+ *    kernels, so the 8 MiB are taken at initialisation and no module load can
+ *    happen at decode time: call dl4s_cuda_init before the host claims the rest
+ *    of HBM and before any stream capture. One host thread per device, as for
+ *    every other call.
+ *  - A key length above Lmax is read as Lmax (all entry points of this path).
  *  - All calls share the one array, and it keeps the previous call's contents.
  *    Nothing in it has to start at zero (every record a call reads is written
  *    by that call first), but two calls that overlap on the GPU - different
@@ -308,6 +355,45 @@ dl4s_status dl4s_cuda_mha_output_forward(const void *d_heads, const float *d_res
                                          float *d_out, int32_t precision, int32_t half_input,
                                          int64_t groups, int64_t group_stride);
 
+/* ------------------------------------------------------------ a layer that spans GPUs
+ * DL4S is single-device; these calls have no counterpart there. MultiHeadAttention.callAsFunction
+ * (MultiHeadAttention.swift:97-127) with its heads spread over `world` GPUs of one node, one rank per GPU (a
+ * process, or a thread with its own current device). The library owns the NCCL communicator, the second stream the
+ * collective runs on and the gather buffers. NCCL (libnccl.so.2, or the path in DL4S_NCCL_LIB) is loaded when the
+ * first of these calls needs it; hosts without it can use everything else.
+ *   comm_unique_id  rank 0 obtains the 128-byte id and hands it to the other ranks by any means (a file, a socket,
+ *                   the launcher's store).
+ *   comm_init       the calling thread's current device joins as `rank` of `world` (collective: every rank calls
+ *                   it). world == 1 needs no id and no NCCL.
+ *   comm_destroy    leaves the communicator and frees its buffers.
+ *   comm_info       rank, world (0 / 1 if the device never joined) and the NCCL version in use (0: not loaded). */
+#define DL4S_COMM_ID_BYTES 128
+dl4s_status dl4s_cuda_comm_unique_id(uint8_t *id);
+dl4s_status dl4s_cuda_comm_init(int32_t rank, int32_t world, const uint8_t *id);
+dl4s_status dl4s_cuda_comm_destroy(void);
+dl4s_status dl4s_cuda_comm_info(int32_t *rank, int32_t *world, int32_t *nccl_version);
+/* Of the last dl4s_cuda_mha_forward_sharded call on this device (waits for it): the summed device time from "head
+ * outputs written" to "gather finished" over its chunks, and the part of it the compute stream spent waiting for a
+ * gather (the exposed part; the rest ran under the next chunk's kernels). Zeros for a world of one. */
+dl4s_status dl4s_cuda_comm_timing(float *gather_ms, float *exposed_ms);
+/* The head-sharded layer. Every rank passes the FULL input d_x [B,S,D] (replicated), ITS column slices of the
+ * projections d_wq_local, d_wk_local [D,(H/world)*dk], d_wv_local [D,(H/world)*dv] (heads
+ * [rank*H/world, (rank+1)*H/world)), and the full Wo [H*dv,D] and LayerNorm parameters. Rank g runs projections and
+ * attention for its heads on the whole batch, ONE ncclAllGather per batch chunk collects the head outputs of all
+ * ranks (as IEEE half on the tensor-core paths), then rank g applies Wo + residual + LayerNorm to its batch slice of
+ * the chunk. With chunks > 1 the gather of chunk c runs on a second stream under the compute of chunk c+1.
+ * The output stays sharded by batch: d_out holds the rows this rank owns, [rows, S, D];
+ * dl4s_cuda_mha_sharded_plan reports how many (and, if batch_index is not NULL, which batch elements, in output
+ * order) for a rank of a world with the same B and chunks; it is host arithmetic and needs no device. Every rank must make the same calls in the same order with the same B, S, chunks
+ * (each call contains collectives). Self-attention only; the mask is structural (d_key_lengths[B] and/or causal). */
+dl4s_status dl4s_cuda_mha_forward_sharded(const float *d_x, int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk, int64_t dv,
+                                          const float *d_wq_local, const float *d_wk_local, const float *d_wv_local,
+                                          const float *d_wo, const float *d_ln_scale, const float *d_ln_shift,
+                                          const int32_t *d_key_lengths, int32_t causal, float *d_out,
+                                          int32_t precision, int32_t chunks);
+dl4s_status dl4s_cuda_mha_sharded_plan(int64_t B, int32_t world, int32_t rank, int32_t chunks, int64_t *rows,
+                                       int64_t *batch_index);
+
 /* One step of incremental decoding through a decoder self-attention layer with a key/value cache: the caller of
  * dl4s_cuda_sdpa_decode. DL4S has no cache — Transformer.callAsFunction(inputSequence:...)
  * (NN/Models/Transformer/Transformer.swift:118-137) re-runs the whole decoder on the growing prefix for every
@@ -353,6 +439,23 @@ dl4s_status dl4s_cuda_encoder_forward(const float *d_x, int64_t B, int64_t S, in
                                       int64_t dk, int64_t dv, int64_t F, int64_t layers,
                                       const float *d_params, const int32_t *d_lengths, int32_t act,
                                       float *d_out, int32_t precision);
+
+/* The same forward with the tensor-core weights converted once instead of on every call. DL4S keeps parameters as
+ * fp32 tensors (TransformerEncoder.swift:29-59); the half (or two-half) copies the tensor cores read do not change
+ * between inference calls, so a caller prepares them once per model:
+ *   prepare  converts Wq|Wk|Wv, Wo, W1, W2 of all layers of d_params (layout as above) for `precision`
+ *            (DL4S_PREC_F16 or DL4S_PREC_F16_SPLIT) into device memory owned by the handle. d_params must stay
+ *            valid: biases and LayerNorm parameters are read from it on every forward.
+ *   refresh  converts again after the parameters changed (an optimiser step).
+ *   forward  is dl4s_cuda_encoder_forward without the conversion pass; shapes outside the tensor-core pipeline
+ *            are refused with DL4S_ERR_UNSUPPORTED.
+ *   destroy  frees the copies (after graphs that recorded a forward with them are destroyed). */
+dl4s_status dl4s_cuda_encoder_prepare(int64_t D, int64_t H, int64_t dk, int64_t dv, int64_t F, int64_t layers,
+                                      const float *d_params, int32_t precision, void **prepared);
+dl4s_status dl4s_cuda_encoder_prepared_refresh(void *prepared);
+dl4s_status dl4s_cuda_encoder_prepared_destroy(void *prepared);
+dl4s_status dl4s_cuda_encoder_forward_prepared(void *prepared, const float *d_x, int64_t B, int64_t S,
+                                               const int32_t *d_lengths, int32_t act, float *d_out);
 
 /* Transformer.prepareInputs (NN/Models/Transformer/Transformer.swift:82-88) with
  * Embedding (NN/Layer/Embedding.swift:152-165) and PositionalEncoding

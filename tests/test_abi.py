@@ -63,3 +63,40 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".cpp", ".swift")):
                 text = open(os.path.join(dirpath, f), errors="ignore").read()
                 assert not pat.search(text), f"{f} reaches into the oracle"
+
+
+def test_injected_failures_travel_through_status_and_last_error(lib_path):
+    """Host-side failure injection (dl4s_cuda_inject_failure): allocation, a host-to-device copy and communicator
+    creation fail with the status a real failure would carry and a message on this thread's last error; the
+    injection is consumed by the call it fails. Needs no device."""
+    from dl4s_b200 import _lib
+    lib = _lib.load()
+    OOM, CUDA, NCCL = -2, -3, -7
+    p = ctypes.c_void_p(123)
+    assert lib.dl4s_cuda_inject_failure(1, 1) == 0
+    assert lib.dl4s_cuda_malloc(1 << 20, ctypes.byref(p)) == OOM
+    assert b"injected failure" in lib.dl4s_cuda_last_error() and not p.value
+    # consumed: the next call fails for the ordinary reason here (no device) or succeeds (on a GPU box)
+    st = lib.dl4s_cuda_malloc(16, ctypes.byref(p))
+    assert st != OOM or b"injected" not in lib.dl4s_cuda_last_error()
+    if st == 0:
+        assert lib.dl4s_cuda_free(p) == 0
+    buf = (ctypes.c_float * 4)()
+    assert lib.dl4s_cuda_inject_failure(2, 2) == 0
+    assert lib.dl4s_cuda_memcpy_h2d(ctypes.c_void_p(16), buf, 16) == CUDA
+    assert lib.dl4s_cuda_memcpy_h2d_async(ctypes.c_void_p(16), buf, 16) == CUDA
+    assert b"host-to-device" in lib.dl4s_cuda_last_error()
+    assert lib.dl4s_cuda_inject_failure(3, 1) == 0
+    ident = (ctypes.c_uint8 * 128)()
+    assert lib.dl4s_cuda_comm_init(0, 2, ident) == NCCL
+    assert b"communicator creation refused" in lib.dl4s_cuda_last_error()
+    assert lib.dl4s_cuda_inject_failure(99, 1) != 0
+    for kind in (1, 2, 3, 4):
+        assert lib.dl4s_cuda_inject_failure(kind, 0) == 0
+    raised = None
+    try:
+        lib.dl4s_cuda_inject_failure(1, 1)
+        _lib.call("dl4s_cuda_malloc", 64, ctypes.byref(p))
+    except _lib.DL4SCudaError as e:      # what the Python mirror (and the Swift glue's fatalError) surface
+        raised = e
+    assert raised is not None and raised.status == OOM and "injected failure" in str(raised)

@@ -129,6 +129,20 @@ def test_decode_against_oracle(dev, oracle, B, H, L, d, min_len):
     assert_fp32(got, oracle.sdpa(q, k2, v2), "decode without lengths")
 
 
+def test_decode_length_beyond_the_cache_is_clamped(dev, oracle):
+    """A device-side length above Lmax reads the Lmax rows that exist (the prefill and fp32 kernels clamp the same way);
+    Lmax is not a multiple of the 256-key chunk, so an unclamped length would walk past the last head's rows."""
+    rng = np.random.default_rng(17)
+    B, H, L, d = 2, 3, 300, 128
+    q, k, v = rand_qkv(rng, B, H, 1, L, d, d)
+    lens = np.array([L + 5, 120], np.int32)
+    from dl4s_b200.layers import ScaledDotProductAttention
+    attn = ScaledDotProductAttention(float(np.sqrt(np.float32(d))))
+    got = attn(dev.tensor(q), dev.tensor(k), dev.tensor(v), dev.StructuredMask(lens, max_len=L)).numpy()
+    want = oracle.sdpa(q, k, v, oracle.make_encoder_mask(np.minimum(lens, L), L))
+    assert_fp32(got, want, "decode with a length above Lmax")
+
+
 def test_decode_length_zero_is_uniform(dev):
     rng = np.random.default_rng(16)
     q, k, v = rand_qkv(rng, 2, 2, 1, 300, 128, 128)

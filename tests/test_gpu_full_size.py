@@ -3,8 +3,8 @@
 The CPU engine cannot finish these in test time, so each case is checked (a) through properties that do not depend on
 the size and (b) against an exact float64 evaluation of sampled outputs (one query row of one head needs only that
 head's keys and values), and the encoder against the float64 numpy formulation of the same op sequence (BLAS makes
-the full configuration a matter of seconds). Tolerances are those of the tensor-core path: max-abs 2e-3 (scaled by
-max(1, |want|)) and relative L2 1e-3; the decode kernels are fp32 and held to 1e-5."""
+the full configuration a matter of seconds). Tolerances are those of the tensor-core path, unscaled: max-abs 2e-3 and
+relative L2 1e-3; the decode kernels are fp32 and held to 1e-5."""
 import numpy as np
 import pytest
 
@@ -81,16 +81,37 @@ def test_decode_full_size(dev):
     assert worst <= 1e-5, f"decode differs from the exact value by {worst:.2e}"
 
 
-def test_encoder_full_size(dev):
-    """The 6-layer encoder at batch 32, seq 512 (padding mask) on the tensor-core path against the float64 numpy
-    formulation of the same op sequence."""
+# Measured error of the 6-layer encoder at batch 32, seq 512 with single-rounded weights (DL4S_PREC_F16): relative L2
+# 6.7e-4 (inside 1e-3), max-abs 3.1e-3 on outputs up to |x| = 5 (OUTSIDE the 2e-3 bound). The bound below is that
+# documented figure with a margin for clock-dependent tile order, not a tolerance of the path: the mode that meets
+# the stated tolerance at this depth is DL4S_PREC_F16_SPLIT.
+F16_ENCODER6_MAX_ABS_DOCUMENTED = 3.5e-3
+
+
+@pytest.mark.parametrize("prec", ["f16", "f16_split"])
+def test_encoder_full_size(dev, oracle, prec):
+    """The 6-layer encoder at batch 32, seq 512 (padding mask) on the tensor-core paths against the float64 numpy
+    formulation of the same op sequence (all 32 sequences) and against the C restatement of the CPU engine on two
+    of them (sequences do not interact, so a sequence's output does not depend on the batch it is in)."""
+    from dl4s_b200 import PREC_F16_SPLIT
     from dl4s_b200.layers import TransformerEncoder
     from oracle import oracle_np as ON
     c = workloads.encoder_config()
-    enc = TransformerEncoder(6, c["heads"], c["dk"], c["dv"], 512, c["F"], layers=c["layers"], precision=PREC_F16)
+    p = PREC_F16 if prec == "f16" else PREC_F16_SPLIT
+    enc = TransformerEncoder(6, c["heads"], c["dk"], c["dv"], 512, c["F"], layers=c["layers"], precision=p)
     got = enc(dev.tensor(c["x"]), c["lengths"]).numpy()
+    assert dev.device_status() == 0
     want = ON.encoder(c["x"], c["layers"], c["heads"], c["lengths"])
     assert np.isfinite(got).all()
     ma, rl = max_abs(got, want), rel_l2(got, want)
-    print(f"encoder 6 x [32,512,512]: max-abs {ma:.3e}, rel-L2 {rl:.3e}")
-    assert rl <= TC_REL_L2 and ma <= TC_MAX_ABS * max(1.0, float(np.abs(want).max())), (ma, rl)
+    print(f"encoder 6 x [32,512,512] {prec}: max-abs {ma:.3e}, rel-L2 {rl:.3e} (max |want| {np.abs(want).max():.2f})")
+    # the CPU engine itself (fp32, reference evaluation order) on the longest and on a padded sequence
+    pick = [0, int(np.argmin(c["lengths"]))]
+    want_c = oracle.encoder(c["x"][pick], c["layers"], c["heads"], c["lengths"][pick])
+    ma_c, rl_c = max_abs(got[pick], want_c), rel_l2(got[pick], want_c)
+    print(f"  against the C restatement on sequences {pick}: max-abs {ma_c:.3e}, rel-L2 {rl_c:.3e}")
+    assert rl <= TC_REL_L2 and rl_c <= TC_REL_L2, (rl, rl_c)
+    if prec == "f16_split":
+        assert ma <= TC_MAX_ABS and ma_c <= TC_MAX_ABS, (ma, ma_c)
+    else:
+        assert ma <= F16_ENCODER6_MAX_ABS_DOCUMENTED and ma_c <= F16_ENCODER6_MAX_ABS_DOCUMENTED, (ma, ma_c)

@@ -3,7 +3,7 @@ through the C ABI against the CPU oracle, in both arithmetic modes."""
 import numpy as np
 import pytest
 
-from dl4s_b200 import ACT_RELU, PREC_F16, PREC_FP32
+from dl4s_b200 import ACT_RELU, PREC_F16, PREC_F16_SPLIT, PREC_FP32
 from dl4s_b200 import workloads
 from util import assert_fp32, assert_tc, golden, max_abs, unpack_layers
 
@@ -45,7 +45,7 @@ def test_layernorm_chunked_statistics(dev, oracle):
     assert np.abs(got.reshape(4, -1).mean(axis=1)).max() < 1e-5
 
 
-@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16], ids=["fp32", "f16"])
+@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16, PREC_F16_SPLIT], ids=["fp32", "f16", "f16_split"])
 def test_mha_golden(dev, prec):
     from dl4s_b200.layers import MultiHeadAttention
     g = golden()
@@ -55,7 +55,7 @@ def test_mha_golden(dev, prec):
     check(prec, mha(x, x, x, dev.makeEncoderMasks(g["causal_lens"])).numpy(), g["mha_out"], "mha golden")
 
 
-@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16], ids=["fp32", "f16"])
+@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16, PREC_F16_SPLIT], ids=["fp32", "f16", "f16_split"])
 def test_mha_config1_full_size(dev, oracle, prec):
     """MultiHeadAttention forward, batch 8, seq 128, d_model 512, 8 heads, no mask, compared elementwise."""
     from dl4s_b200.layers import MultiHeadAttention
@@ -107,7 +107,7 @@ def test_mha_cross_attention_and_masks(dev, oracle, prec):
     check(prec, got, want, "decoder self-attention")
 
 
-@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16], ids=["fp32", "f16"])
+@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16, PREC_F16_SPLIT], ids=["fp32", "f16", "f16_split"])
 def test_ffn(dev, oracle, prec):
     from dl4s_b200.layers import PointwiseFeedForward
     g = golden()
@@ -125,7 +125,7 @@ def test_ffn(dev, oracle, prec):
     check(prec, ffn(dev.tensor(xb)).numpy(), want, "ffn 256->1024")
 
 
-@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16], ids=["fp32", "f16"])
+@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16, PREC_F16_SPLIT], ids=["fp32", "f16", "f16_split"])
 def test_encoder_golden_and_midsize(dev, oracle, prec):
     from dl4s_b200.layers import TransformerEncoder
     g = golden()
@@ -138,6 +138,76 @@ def test_encoder_golden_and_midsize(dev, oracle, prec):
     got = enc(dev.tensor(c["x"]), c["lengths"]).numpy()
     want = oracle.encoder(c["x"], c["layers"], 8, c["lengths"])
     check(prec, got, want, "encoder 2 x [2,128,512]")
+
+
+@pytest.mark.parametrize("prec", [PREC_F16, PREC_F16_SPLIT], ids=["f16", "f16_split"])
+def test_encoder_prepared_weights(dev, oracle, prec):
+    """Weights converted once (dl4s_cuda_encoder_prepare) give the same bytes as the per-call conversion of
+    dl4s_cuda_encoder_forward, follow a refresh after the parameters changed, and the split form is the more
+    exact one."""
+    import ctypes
+    from dl4s_b200._lib import c_vp, call
+    from dl4s_b200.layers import TransformerEncoder
+    c = workloads.encoder_config(B=2, S=128, D=512, H=8, F=2048, layers=2, vocab=1000)
+    enc = TransformerEncoder(2, 8, 64, 64, 512, 2048, layers=c["layers"], precision=prec)
+    x, mask = dev.tensor(c["x"]), dev.makeEncoderMasks(c["lengths"])
+    prepared = enc(x, mask).numpy()                  # the layer class prepares on first use
+    assert prec in enc._prepared
+    plain = dev.CUDA.Memory.allocateBuffer(c["x"].shape)
+    call("dl4s_cuda_encoder_forward", c_vp(x.ptr), 2, 128, 512, 8, 64, 64, 2048, 2, c_vp(enc.params.ptr), c_vp(mask.lengths.ptr), 0,
+         c_vp(plain.ptr), prec)
+    assert np.array_equal(plain.numpy(), prepared)
+    # new parameter values in the same block: stale copies until refreshed
+    c2 = workloads.encoder_config(B=2, S=128, D=512, H=8, F=2048, layers=2, vocab=1000, seed_w=77)
+    enc2 = TransformerEncoder(2, 8, 64, 64, 512, 2048, layers=c2["layers"], precision=prec)
+    dev.CUDA.Memory.assign(enc2.params, enc.params, enc.params.count)
+    enc.weightsChanged()
+    assert np.array_equal(enc(x, mask).numpy(), enc2(x, mask).numpy())
+    want = oracle.encoder(c["x"], c2["layers"], 8, c["lengths"])
+    check(prec, enc(x, mask).numpy(), want, "after refresh")
+    enc.releasePreparedWeights()
+    assert dev.device_status() == 0
+
+
+def test_split_weights_are_more_exact(dev, oracle):
+    from dl4s_b200.layers import TransformerEncoder
+    from util import rel_l2
+    c = workloads.encoder_config(B=2, S=128, D=512, H=8, F=2048, layers=2, vocab=1000)
+    want = oracle.encoder(c["x"], c["layers"], 8, c["lengths"])
+    errs = {}
+    for prec in (PREC_F16, PREC_F16_SPLIT):
+        enc = TransformerEncoder(2, 8, 64, 64, 512, 2048, layers=c["layers"], precision=prec)
+        errs[prec] = rel_l2(enc(dev.tensor(c["x"]), c["lengths"]).numpy(), want)
+    assert errs[PREC_F16_SPLIT] < 0.8 * errs[PREC_F16], errs
+
+
+def test_operation_group_trace(dev):
+    """The reference's OperationGroup names (Tensor/Graph.swift:134-163) around the launches they cover: with tracing
+    on, one encoder forward enters Encoder > EncoderLayer > MultiHeadAttention > ScaledDotProductAttention /
+    LayerNorm and PointwiseFeedForward > Dense / LayerNorm, once per layer, in order."""
+    import ctypes
+    from dl4s_b200._lib import call
+    from dl4s_b200.layers import TransformerEncoder
+    c = workloads.encoder_config(B=2, S=128, D=512, H=8, F=2048, layers=2, vocab=1000)
+    enc = TransformerEncoder(2, 8, 64, 64, 512, 2048, layers=c["layers"], precision=PREC_F16)
+    x, mask = dev.tensor(c["x"]), dev.makeEncoderMasks(c["lengths"])
+    enc(x, mask)
+    call("dl4s_cuda_set_trace", 1)
+    try:
+        enc(x, mask)
+        buf = ctypes.create_string_buffer(1 << 16)
+        call("dl4s_cuda_trace_read", buf, len(buf))
+    finally:
+        call("dl4s_cuda_set_trace", 0)
+    paths = buf.value.decode().split()
+    layer = ["Encoder/EncoderLayer", "Encoder/EncoderLayer/MultiHeadAttention",
+             "Encoder/EncoderLayer/MultiHeadAttention/ScaledDotProductAttention",
+             "Encoder/EncoderLayer/MultiHeadAttention/LayerNorm", "Encoder/EncoderLayer/PointwiseFeedForward",
+             "Encoder/EncoderLayer/PointwiseFeedForward/Dense", "Encoder/EncoderLayer/PointwiseFeedForward/Dense",
+             "Encoder/EncoderLayer/PointwiseFeedForward/LayerNorm"]
+    assert paths == ["Encoder"] + layer * 2, paths
+    call("dl4s_cuda_trace_read", buf, len(buf))
+    assert buf.value == b""
 
 
 def test_encoder_blocks_compose_like_the_single_call(dev):
@@ -214,23 +284,20 @@ def test_mha_halves_emulate_head_sharding_on_one_gpu(dev, oracle, prec, half):
         assert np.array_equal(out2.numpy(), out.numpy()), f"rank {g}: grouped read differs from rebuilt rows"
 
 
-def test_head_sharded_layer_world_size_one(dev, oracle):
-    """HeadShardedMultiHeadAttention without a process group is the plain layer."""
-    pytest.importorskip("torch")
-    import torch
+@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16], ids=["fp32", "f16"])
+def test_head_sharded_layer_world_size_one(dev, oracle, prec):
+    """dl4s_cuda_mha_forward_sharded on a device that joined no communicator is the plain layer."""
     from dl4s_b200.sharded import HeadShardedMultiHeadAttention
-    c = workloads.mha_config(B=2, S=64, D=256, H=4)
-    layer = HeadShardedMultiHeadAttention(4, 256, 64, 64, c["weights"], precision=PREC_FP32)
-    stream = torch.cuda.Stream()
-    with torch.cuda.stream(stream):
-        dev.set_stream(stream.cuda_stream)
-        got = layer(dev.tensor(c["x"]), dev.StructuredMask(None, causal=True)).numpy()
-        dev.set_stream(None)
+    c = workloads.mha_config(B=3, S=128, D=256, H=4)
+    layer = HeadShardedMultiHeadAttention(4, 256, 64, 64, c["weights"], precision=prec, chunks=2)
+    assert (layer.rank, layer.world) == (0, 1) and layer.owned_batches(3) == [0, 1, 2]
+    got = layer(dev.tensor(c["x"]), dev.StructuredMask(None, causal=True)).numpy()
     w = c["weights"]
     one, zero = np.ones(256, np.float32), np.zeros(256, np.float32)
     want = oracle.mha(c["x"], c["x"], c["x"], w["qDense"], w["kDense"], w["vDense"], w["fc"], one, zero, 4,
-                      oracle.make_decoder_mask(np.full(2, 64, np.int32), 64))
-    assert_fp32(got, want, "world size 1")
+                      oracle.make_decoder_mask(np.full(3, 128, np.int32), 128))
+    check(prec, got, want, "world size 1")
+    assert dev.device_status() == 0
 
 
 def test_half_head_outputs_are_refused_off_the_tensor_core_path(dev):
@@ -280,6 +347,34 @@ def test_graph_replay_equals_eager(dev, oracle):
         with dev.Graph() as g2:
             dev.CUDA.Memory.allocateBuffer((4,))
     g2.destroy()
+    assert dev.device_status() == 0
+
+
+def test_graph_survives_a_larger_eager_call(dev, oracle):
+    """A recorded graph names the library's scratch arena by address. A later eager call with a larger shape makes
+    the arena grow; the old block must stay allocated until the graph is destroyed, so the replay still computes
+    the recorded forward."""
+    from dl4s_b200.layers import MultiHeadAttention
+    c = workloads.mha_config(B=2, S=128, D=512, H=8)
+    small = MultiHeadAttention(8, 512, 64, 64, weights=c["weights"], precision=PREC_F16)
+    x = dev.tensor(c["x"])
+    out = dev.CUDA.Memory.allocateBuffer(c["x"].shape)
+    small(x, x, x, out=out)
+    eager = out.numpy()
+    with dev.Graph() as g:
+        small(x, x, x, out=out)
+    # a much larger layer: the arena is replaced
+    big_c = workloads.mha_config(B=16, S=512, D=1024, H=8, seed_x=5, seed_w=6)
+    big = MultiHeadAttention(8, 1024, 128, 128, weights=big_c["weights"], precision=PREC_F16)
+    xb = dev.tensor(big_c["x"])
+    big(xb, xb, xb)
+    dev.CUDA.Memory.assign(dev.tensor(np.zeros_like(c["x"])), out, out.count)
+    g.launch()
+    assert np.array_equal(out.numpy(), eager)
+    big(xb, xb, xb)            # the new arena is in use between replays
+    g.launch()
+    assert np.array_equal(out.numpy(), eager)
+    g.destroy()
     assert dev.device_status() == 0
 
 

@@ -3,7 +3,7 @@ the DL4S CPU engine's semantics (Engine/CPU/CPUEngine.swift)."""
 import numpy as np
 import pytest
 
-from util import assert_fp32, max_abs
+from util import assert_fp32_rel, max_abs
 
 pytestmark = pytest.mark.gpu
 
@@ -54,7 +54,7 @@ def test_elementwise(dev):
             if fn is E.sqrt: src = up(dev, np.abs(a))
             if fn is E.log: src = up(dev, np.abs(a) + 1)
             fn(src, out)
-            assert_fp32(out.numpy(), ref, fn.__name__)
+            assert_fp32_rel(out.numpy(), ref, fn.__name__)
         E.fill(2.5, out)
         assert (out.numpy() == 2.5).all()
     # log(exp(x)) ~ x at 1e-4, the reference's own check (VecTests.swift:158-168)
@@ -98,7 +98,7 @@ def test_reduce(dev, shape, axes):
     rshape = tuple(s for i, s in enumerate(shape) if i not in axes)
     out = dev.CUDA.Memory.allocateBuffer(rshape or (1,))
     E.reduceSum(ta, out, axes=axes)
-    assert_fp32(out.numpy().reshape(rshape), a.astype(np.float64).sum(axis=tuple(axes)), "reduceSum")
+    assert_fp32_rel(out.numpy().reshape(rshape), a.astype(np.float64).sum(axis=tuple(axes)), "reduceSum")
     E.reduceMax(ta, out, axes=axes)
     assert np.array_equal(out.numpy().reshape(rshape), a.max(axis=tuple(axes)))
     if len(axes) == 1:
@@ -131,6 +131,19 @@ def test_stack_and_band(dev):
     same = [rng.standard_normal((2, 4, 3)).astype(np.float32) for _ in range(3)]
     E.stack([up(dev, p) for p in same], out0, axis=0)
     assert np.array_equal(out0.numpy(), np.concatenate(same, axis=0))
+    # unstack / unstackAdd are the inverse (Engine.swift:543,551)
+    back = [dev.CUDA.Memory.allocateBuffer(p.shape) for p in parts]
+    E.unstack(out, back, axis=1)
+    for b_, p in zip(back, parts):
+        assert np.array_equal(b_.numpy(), p)
+    adds = [rng.standard_normal(p.shape).astype(np.float32) for p in parts]
+    E.unstackAdd(out, [up(dev, a) for a in adds], back, axis=1)
+    for b_, p, a in zip(back, parts, adds):
+        assert np.array_equal(b_.numpy(), p + a)
+    back0 = [dev.CUDA.Memory.allocateBuffer(p.shape) for p in same]
+    E.unstack(out0, back0, axis=0)
+    for b_, p in zip(back0, same):
+        assert np.array_equal(b_.numpy(), p)
     ones = np.ones((5, 7), np.float32)
     b = dev.CUDA.Memory.allocateBuffer((5, 7))
     E.band(up(dev, ones), b, belowDiagonal=-1, aboveDiagonal=None)   # the causal mask of makeDecoderMasks
@@ -152,12 +165,12 @@ def test_gemm_fp32_all_transposes(dev, oracle, M, N, K):
             b = B.T.copy() if tb else B
             out = dev.CUDA.Memory.allocateBuffer((M, N))
             E.gemm(up(dev, a), up(dev, b), out, transposeFirst=ta, transposeSecond=tb)
-            assert_fp32(out.numpy(), oracle.gemm(a, b, trans_a=ta, trans_b=tb), f"gemm ta={ta} tb={tb}")
+            assert_fp32_rel(out.numpy(), oracle.gemm(a, b, trans_a=ta, trans_b=tb), f"gemm ta={ta} tb={tb}")
     # alpha / beta
     C0 = rng.standard_normal((M, N)).astype(np.float32)
     out = up(dev, C0)
     E.gemm(up(dev, A), up(dev, B), out, alpha=0.5, beta=2.0)
-    assert_fp32(out.numpy(), 0.5 * (A.astype(np.float64) @ B.astype(np.float64)) + 2.0 * C0, "alpha/beta")
+    assert_fp32_rel(out.numpy(), 0.5 * (A.astype(np.float64) @ B.astype(np.float64)) + 2.0 * C0, "alpha/beta")
 
 
 def test_gemm_known_answers_from_reference_tests(dev):
@@ -203,3 +216,71 @@ def test_gemm_tensor_core_shapes(dev, M, N, K):
     # twice in a row: the work counters are left clean by the first launch
     E.gemm(up(dev, A), up(dev, B), out, precision=PREC_F16)
     assert np.array_equal(out.numpy(), got)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (1000, 512, 256), (4096 + 77, 1536, 512), (300, 256, 1024), (2048, 192, 320)])
+def test_gemm_split_weights(dev, M, N, K):
+    """DL4S_PREC_F16_SPLIT: the second operand enters as two halves (rounded value + rounded remainder), so only the
+    first operand's rounding remains. Checked against the float64 product of the half-rounded A with the exact B:
+    the error must be far below what rounding B once would leave."""
+    from dl4s_b200 import PREC_F16, PREC_F16_SPLIT
+    E = dev.CUDA.Engine
+    rng = np.random.default_rng(M * 3 + N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) * 0.1).astype(np.float32)
+    out = dev.CUDA.Memory.allocateBuffer((M, N))
+    E.gemm(up(dev, A), up(dev, B), out, precision=PREC_F16_SPLIT)
+    got = out.numpy()
+    Ah = A.astype(np.float16).astype(np.float64)
+    want = Ah @ B.astype(np.float64)
+    single = Ah @ B.astype(np.float16).astype(np.float64)
+    err, err_single = np.abs(got - want).max(), np.abs(single - want).max()
+    assert err <= 2e-5 * max(1.0, np.abs(want).max()) * np.sqrt(K), f"max error {err} vs the product with the exact second operand"
+    assert err < 0.1 * err_single, f"split weights leave {err}, single-rounded weights {err_single}"
+    assert dev.device_status() == 0
+
+
+def test_operand_outside_the_half_range_is_reported(dev):
+    """A tensor-core operand at or above 65504 becomes infinite when rounded to half: the conversion sets a bit in
+    the device status word, which reads back as an error and is cleared by the read."""
+    from dl4s_b200 import DL4SCudaError, PREC_F16
+    E = dev.CUDA.Engine
+    A = np.ones((128, 64), np.float32)
+    A[5, 7] = 1e5
+    B = np.ones((64, 128), np.float32)
+    out = dev.CUDA.Memory.allocateBuffer((128, 128))
+    E.gemm(up(dev, A), up(dev, B), out, precision=PREC_F16)
+    with pytest.raises(DL4SCudaError) as e:
+        dev.device_status()
+    assert "half range" in str(e.value) and e.value.status == -1
+    assert dev.device_status() == 0
+    # the same values are fine in fp32
+    E.gemm(up(dev, A), up(dev, B), out)
+    assert dev.device_status() == 0
+    assert out.numpy()[5, 0] == np.float32(1e5 + 63)
+
+
+def test_bounded_wait_runs_out_and_is_reported(dev):
+    """A bounded device-side wait that runs out: the next single-CTA tensor-core product is told to leave out one
+    operand load and to poll with a short limit. Its MMA thread's wait on that stage gives up, every role leaves
+    through the kernel's normal exit (tensor memory freed, nothing traps or spins), the status word reads back as
+    DL4S_ERR_TIMEOUT, and the device works normally afterwards."""
+    from dl4s_b200 import DL4SCudaError, PREC_F16
+    from dl4s_b200._lib import call
+    E = dev.CUDA.Engine
+    rng = np.random.default_rng(8)
+    A = rng.standard_normal((128, 128)).astype(np.float32)
+    B = rng.standard_normal((128, 128)).astype(np.float32)
+    a, b = up(dev, A), up(dev, B)
+    out = dev.CUDA.Memory.allocateBuffer((128, 128))
+    assert dev.device_status() == 0
+    call("dl4s_cuda_inject_failure", 4, 1)
+    E.gemm(a, b, out, precision=PREC_F16)          # one tile, one CTA, two k-blocks: the second is never loaded
+    with pytest.raises(DL4SCudaError) as e:
+        dev.device_status()
+    assert e.value.status == -5 and "wait gave up" in str(e.value)
+    assert dev.device_status() == 0                # cleared by the read
+    E.gemm(a, b, out, precision=PREC_F16)          # the same launch without the fault
+    want = A.astype(np.float16).astype(np.float64) @ B.astype(np.float16).astype(np.float64)
+    assert np.abs(out.numpy() - want).max() <= 1e-3
+    assert dev.device_status() == 0

@@ -121,6 +121,28 @@ def test_ranges_cover_everything():
         sharded.head_range(6, 4, 0)
 
 
+def test_library_plan_equals_the_python_statement():
+    """dl4s_cuda_mha_sharded_plan (host arithmetic inside the library, the split dl4s_cuda_mha_forward_sharded uses)
+    against the index helpers the gloo ranks above are checked with."""
+    import ctypes
+    sys.path.insert(0, ROOT)
+    from dl4s_b200 import sharded
+    from dl4s_b200._lib import call
+    for world in (1, 2, 4, 8):
+        for B in (1, 5, 8, 256):
+            for chunks in (1, 3, 4, 64, 300):
+                seen = []
+                for r in range(world):
+                    rows = ctypes.c_int64(-1)
+                    idx = (ctypes.c_int64 * B)()
+                    call("dl4s_cuda_mha_sharded_plan", B, world, r, chunks, ctypes.byref(rows), idx)
+                    got = [int(idx[i]) for i in range(rows.value)]
+                    want = sharded.owned_batches(B, world, r, min(chunks, 64) if world > 1 else 1)
+                    assert got == want, (world, B, chunks, r)
+                    seen += got
+                assert sorted(seen) == list(range(B))
+
+
 def test_rows_from_groups_is_the_rank_major_gather_read_in_place():
     sys.path.insert(0, ROOT)
     from dl4s_b200 import sharded

@@ -4,7 +4,7 @@ dl4s_cuda_sdpa_decode_noalloc serves hosts that cannot call cudaMalloc where dec
 handed to their own cache manager, or a step that cannot take cudaMalloc's device-wide synchronisation). Its
 split-K records live in a fixed array inside the library instead of the growing scratch arena. The array is
 shared by all calls and keeps the previous call's contents, so the check runs two different problems back to
-back and compares each with the allocating entry point, which the other tests pin to the CPU oracle.
+back and compares each with the allocating entry point and with the CPU oracle.
 """
 import ctypes
 
@@ -31,7 +31,13 @@ def _decode_both(dev, q, k, v, lens):
     return out.numpy(), ref.numpy()
 
 
-def test_noalloc_decode_matches_allocating_entry_point_twice_in_a_row(dev):
+def _oracle_decode(oracle, q, k, v, lens):
+    L = k.shape[2]
+    mask = None if lens is None else oracle.make_encoder_mask(np.clip(lens, 0, L), L)
+    return oracle.sdpa(q, k, v, mask)
+
+
+def test_noalloc_decode_matches_allocating_entry_point_twice_in_a_row(dev, oracle):
     rng = np.random.default_rng(99)
     # first call: long ragged contexts, many split-K records
     B, H, L, d = 3, 4, 3000, 128
@@ -41,6 +47,7 @@ def test_noalloc_decode_matches_allocating_entry_point_twice_in_a_row(dev):
     lens = np.array([3000, 1, 1777], np.int32)
     got, want = _decode_both(dev, q, k, v, lens)
     assert_close(got, want, FP32_TOL, FP32_TOL, "first call")
+    assert_close(got, _oracle_decode(oracle, q, k, v, lens), FP32_TOL, FP32_TOL, "first call against the CPU oracle")
     # second call right after: a different, smaller problem whose records overlay the first call's leftovers
     B, H, L, d = 2, 3, 700, 64
     q = rng.standard_normal((B, H, 1, d), dtype=np.float32)
@@ -48,6 +55,7 @@ def test_noalloc_decode_matches_allocating_entry_point_twice_in_a_row(dev):
     v = rng.standard_normal((B, H, L, d), dtype=np.float32) + 5
     got, want = _decode_both(dev, q, k, v, None)
     assert_close(got, want, FP32_TOL, FP32_TOL, "second call")
+    assert_close(got, _oracle_decode(oracle, q, k, v, None), FP32_TOL, FP32_TOL, "second call against the CPU oracle")
     assert dev.device_status() == 0
 
 
@@ -80,3 +88,18 @@ def test_noalloc_decode_rejects_oversized_problems(dev):
         call("dl4s_cuda_sdpa_decode_noalloc", c_vp(buf.ptr), c_vp(buf.ptr), c_vp(buf.ptr), 1, 1, 128, 96, c_f32(1.0), c_vp(0),
              c_vp(buf.ptr))
     assert dev.launch_count() == n0
+    # an empty batch is a no-op, as for the allocating entry point
+    call("dl4s_cuda_sdpa_decode_noalloc", c_vp(buf.ptr), c_vp(buf.ptr), c_vp(buf.ptr), 0, 4, 128, 128, c_f32(1.0), c_vp(0), c_vp(buf.ptr))
+    assert dev.launch_count() == n0
+
+
+def test_noalloc_decode_clamps_a_length_beyond_the_cache(dev, oracle):
+    rng = np.random.default_rng(101)
+    B, H, L, d = 2, 2, 300, 64
+    q = rng.standard_normal((B, H, 1, d), dtype=np.float32)
+    k = rng.standard_normal((B, H, L, d), dtype=np.float32)
+    v = rng.standard_normal((B, H, L, d), dtype=np.float32)
+    lens = np.array([L + 9, 17], np.int32)
+    got, want = _decode_both(dev, q, k, v, lens)
+    assert_close(got, want, FP32_TOL, FP32_TOL, "clamped length")
+    assert_close(got, _oracle_decode(oracle, q, k, v, lens), FP32_TOL, FP32_TOL, "clamped length against the CPU oracle")

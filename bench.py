@@ -653,8 +653,13 @@ def head_sharded_bench(args, gpu, peaks, shape=None, steps=None, warmup=3):
     total_ms = gpu.timed_steps(step, steps, warmup, flush=False)
     launches = gpu.last_timed_launches
     clocks = sampler.stop()
-    # the collective: device time of the gathers of one step and the part the compute stream waited for (max over ranks)
-    step()
+    # the collective: device time of the gathers of one step and the part the compute stream waited for (max over
+    # ranks). Taken from the last of three back-to-back steps after a barrier, so that the ranks enter it together: a
+    # rank that arrives late shows up as waiting time on the others.
+    gpu.sync()
+    gpu.barrier()
+    for _ in range(3):
+        step()
     gather_ms, exposed_ms = sharded.comm_timing()
     gather_ms, exposed_ms = gpu.max_over_ranks(gather_ms), gpu.max_over_ranks(exposed_ms)
     flops = 3 * 2 * B * S * D * D + 4 * B * H * dk * (S * (S + 1) // 2) + 2 * B * S * D * D

@@ -5,7 +5,7 @@ import pytest
 
 from dl4s_b200 import ACT_RELU, PREC_F16, PREC_F16_SPLIT, PREC_FP32
 from dl4s_b200 import workloads
-from util import assert_fp32, assert_tc, golden, max_abs, unpack_layers
+from util import assert_fp32, assert_fp32_rel, assert_tc, golden, max_abs, unpack_layers
 
 pytestmark = pytest.mark.gpu
 
@@ -246,8 +246,10 @@ def test_mha_halves_emulate_head_sharding_on_one_gpu(dev, oracle, prec, half):
     rng = np.random.default_rng(30)
     G, B, S, D, H, dk = 2, 3, 140, 128, 2, 64
     x = rng.standard_normal((B, S, D), dtype=np.float32)
-    W = {n: (rng.standard_normal((D, H * dk)) * 0.1).astype(np.float32) for n in ("qDense", "kDense", "vDense")}
-    W["fc"] = (rng.standard_normal((H * dk, D)) * 0.1).astype(np.float32)
+    # weights Xavier-uniform and inputs N(0,1): the distributions the stated tolerances are quoted on
+    from dl4s_b200.layers import xavier_uniform
+    W = {n: xavier_uniform(rng, D, H * dk) for n in ("qDense", "kDense", "vDense")}
+    W["fc"] = xavier_uniform(rng, H * dk, D)
     lens = np.array([140, 77, 1], np.int32)
     one, zero = np.ones(D, np.float32), np.zeros(D, np.float32)
     want = oracle.mha(x, x, x, W["qDense"], W["kDense"], W["vDense"], W["fc"], one, zero, H, oracle.make_decoder_mask(lens, S))
@@ -434,17 +436,28 @@ def test_decode_step_reports_a_full_cache(dev):
 
 @pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16], ids=["fp32", "f16"])
 def test_output_head(dev, oracle, prec):
-    """logSoftmax(x . E^T + bias) over the vocabulary against the CPU engine's order of operations."""
+    """logSoftmax(x . E^T + bias) over the vocabulary against the CPU engine's order of operations. The embedding
+    is N(0, 0.02) as in the benchmark configuration and the states are N(0,1) (what a LayerNorm leaves), so the
+    log-probabilities are O(10) and the stated absolute tolerances apply; a last case with logits of O(30) is held
+    to the same bounds relative to the largest |value| (half operands carry a relative error)."""
     from dl4s_b200.layers import EmbeddingWithPositions, OutputHead
+    from util import FP32_TOL, TC_MAX_ABS, TC_REL_L2, assert_close
     rng = np.random.default_rng(50)
-    for B, S, D, V in ((2, 5, 24, 37), (2, 100, 128, 1024), (1, 130, 64, 2048 + 64)):
-        E = (rng.standard_normal((V, D)) * 0.3).astype(np.float32)
+    for B, S, D, V, escale in ((2, 5, 24, 37, 0.02), (2, 100, 128, 1024, 0.02), (1, 130, 64, 2048 + 64, 0.02),
+                               (2, 100, 128, 1024, 0.3)):
+        E = (rng.standard_normal((V, D)) * escale).astype(np.float32)
         bias = (rng.standard_normal(V) * 0.1).astype(np.float32)
         x = rng.standard_normal((B, S, D), dtype=np.float32)
         head = OutputHead(EmbeddingWithPositions(E), bias, precision=prec)
         got = head(dev.tensor(x)).numpy()
         want = oracle.output_head(x, E, bias)
-        check(prec, got, want, f"output head [{B},{S},{D}] x {V}")
+        if escale == 0.02:
+            check(prec, got, want, f"output head [{B},{S},{D}] x {V}")
+        else:
+            big = float(np.abs(want).max())
+            assert big > 10
+            lim = (FP32_TOL * big, FP32_TOL) if prec == PREC_FP32 else (TC_MAX_ABS * big, TC_REL_L2)
+            assert_close(got, want, lim[0], lim[1], f"output head with logits up to {big:.0f} (bound relative to that)")
         assert np.abs(np.exp(got.astype(np.float64)).sum(-1) - 1).max() < 1e-4
         # greedy decoding picks the same token
         assert np.array_equal(got.argmax(-1), want.argmax(-1)) or prec == PREC_F16
@@ -457,4 +470,6 @@ def test_log_softmax_rows_in_place_and_ragged(dev, oracle):
         x = (rng.standard_normal((rows, n)) * 3).astype(np.float32)
         t = dev.tensor(x)
         call("dl4s_cuda_log_softmax_rows", c_vp(t.ptr), rows, n, c_vp(t.ptr))
-        assert_fp32(t.numpy(), oracle.log_softmax_rows(x), f"log-softmax {rows} x {n}")
+        # values of O(20); a sum over 32000 fp32 terms carries ~1e-5 RELATIVE error in either order of summation (the
+        # CPU engine adds them one after the other), so the bound is relative to the largest |value|
+        assert_fp32_rel(t.numpy(), oracle.log_softmax_rows(x), f"log-softmax {rows} x {n}")

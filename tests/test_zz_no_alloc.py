@@ -55,7 +55,10 @@ def test_noalloc_decode_matches_allocating_entry_point_twice_in_a_row(dev, oracl
     v = rng.standard_normal((B, H, L, d), dtype=np.float32) + 5
     got, want = _decode_both(dev, q, k, v, None)
     assert_close(got, want, FP32_TOL, FP32_TOL, "second call")
-    assert_close(got, _oracle_decode(oracle, q, k, v, None), FP32_TOL, FP32_TOL, "second call against the CPU oracle")
+    # values of O(5) summed over 700 keys: the CPU engine's one-after-the-other fp32 sum is itself only good to ~1e-5
+    # absolute here, so against the oracle the bound is relative to the largest |value|
+    want_cpu = _oracle_decode(oracle, q, k, v, None)
+    assert_close(got, want_cpu, FP32_TOL * float(np.abs(want_cpu).max()), FP32_TOL, "second call against the CPU oracle")
     assert dev.device_status() == 0
 
 

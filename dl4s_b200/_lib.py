@@ -88,6 +88,9 @@ _SIGNATURES = {
     "dl4s_cuda_stack": [ctypes.POINTER(c_vp), c_i64p, c_i32, c_i32, c_i32, c_vp],
     "dl4s_cuda_unstack": [c_vp, ctypes.POINTER(c_vp), c_i64p, c_i32, c_i32, c_i32],
     "dl4s_cuda_unstack_add": [c_vp, ctypes.POINTER(c_vp), ctypes.POINTER(c_vp), c_i64p, c_i32, c_i32, c_i32],
+    "dl4s_cuda_dropout": [c_vp, c_vp, c_i64, c_f32, ctypes.c_uint64, ctypes.c_uint32],
+    "dl4s_cuda_set_dropout": [c_f32, ctypes.c_uint64],
+    "dl4s_cuda_dropout_counter": [ctypes.POINTER(ctypes.c_uint32), ctypes.POINTER(ctypes.c_uint32)],
     "dl4s_cuda_band": [c_vp, c_i64, c_i64, c_i32, c_i32, c_i32, c_i32, c_vp],
     "dl4s_cuda_gemm": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_f32, c_f32, c_i32, c_i32, c_i32],
     "dl4s_cuda_sdpa_forward": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_f32, c_vp, c_i32,
@@ -114,6 +117,17 @@ _SIGNATURES = {
     "dl4s_cuda_mha_sharded_plan": [c_i64, c_i32, c_i32, c_i32, c_i64p, c_i64p],
     "dl4s_cuda_mha_decode_step": [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i64,
                                   c_vp, c_vp],
+    "dl4s_cuda_decoder_forward": [c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_i32,
+                                  c_vp, c_i32],
+    "dl4s_cuda_mha_kv_project": [c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_i64],
+    "dl4s_cuda_decoder_cache_create": [c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, ctypes.POINTER(c_vp)],
+    "dl4s_cuda_decoder_cache_set_encoder": [c_vp, c_vp, c_vp],
+    "dl4s_cuda_decoder_cache_lengths": [c_vp, ctypes.POINTER(c_vp)],
+    "dl4s_cuda_decoder_step": [c_vp, c_vp, c_i32, c_vp],
+    "dl4s_cuda_decoder_cache_destroy": [c_vp],
+    "dl4s_cuda_embed_at": [c_vp, c_i64, c_i64, c_i64, c_i64, c_vp, c_i64, c_i32, c_vp],
+    "dl4s_cuda_transformer_greedy_decode": [c_i32p, c_i64, c_i32, c_i32, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64,
+                                            c_vp, c_vp, c_vp, c_i32, c_i32, c_i32, c_i32p, c_i64p],
     "dl4s_cuda_output_head": [c_vp, c_i64, c_i64, c_vp, c_i64, c_vp, c_vp, c_i32],
     "dl4s_cuda_log_softmax_rows": [c_vp, c_i64, c_i64, c_vp],
     "dl4s_cuda_ffn_forward": [c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_i32],

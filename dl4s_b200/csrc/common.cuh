@@ -58,6 +58,11 @@ struct DeviceState {
     bool timing = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float last_ms = 0.f;
+    // Dropout (dl4s_cuda_set_dropout): rate 0 = inactive. Every site that applies dropout takes the next counter
+    // value, so masks differ between sites, layers and calls and a host can regenerate any of them.
+    float dropout_rate = 0.f;
+    uint64_t dropout_seed = 0;
+    uint32_t dropout_counter = 0;
     // Operation-group trace (dl4s_cuda_set_trace): NVTX ranges + a host-side list of the group paths entered.
     bool tracing = false;
     int trace_depth = 0;
@@ -172,6 +177,27 @@ __device__ __forceinline__ void split_hilo(const float4 &v, uint2 &hi, uint2 &lo
 }
 #endif
 
+// ---- dropout (NN/Layer/Dropout.swift:47-55: inputs * bernoulli(1 - rate), no rescaling) ----
+// The reference draws the mask on the host from a process-global generator (Random.swift:148-157) and copies it to
+// the device per call. Here element i of site `counter` is kept when a counter-based hash of (seed, counter, i) is
+// below threshold = (1 - rate) * 2^32: no state, no mask in memory, and the host can compute the same bits.
+struct DropoutSpec {
+    uint32_t threshold = 0;   // 0: dropout inactive, everything is kept
+    uint32_t seed_lo = 0, seed_hi = 0, counter = 0;
+};
+__host__ __device__ __forceinline__ uint32_t dropout_hash(uint64_t index, uint32_t seed_lo, uint32_t seed_hi, uint32_t counter)
+{
+    uint32_t h = (uint32_t)index * 0x9E3779B1u + seed_lo;
+    h ^= h >> 16; h *= 0x85EBCA6Bu; h ^= h >> 13; h *= 0xC2B2AE35u; h ^= h >> 16;
+    h += ((uint32_t)(index >> 32) ^ counter) * 0x27D4EB2Fu + seed_hi;
+    h ^= h >> 15; h *= 0x2C1B3C6Du; h ^= h >> 12; h *= 0x297A2D39u; h ^= h >> 15;
+    return h;
+}
+__host__ __device__ __forceinline__ bool dropout_keep(const DropoutSpec &d, uint64_t index)
+{
+    return d.threshold == 0 || dropout_hash(index, d.seed_lo, d.seed_hi, d.counter) < d.threshold;
+}
+
 // ---- programmatic dependent launch ----
 // Kernels of one pipeline are launched with the programmatic-serialization attribute: the next kernel's CTAs may
 // be scheduled (and run their prologue: barrier set-up, tensor-memory allocation) while the previous kernel is
@@ -213,6 +239,20 @@ inline cudaError_t launch_pdl(DeviceState *st, void (*kernel)(KArgs...), dim3 gr
 }
 #endif
 
+// The spec of the next dropout site on this device (inactive when the rate is 0); takes one counter value.
+inline DropoutSpec next_dropout(DeviceState *st)
+{
+    DropoutSpec d;
+    if (st->dropout_rate > 0.f) {
+        double keep = (1.0 - (double)st->dropout_rate) * 4294967296.0;
+        d.threshold = keep >= 4294967295.0 ? 0xFFFFFFFFu : (keep < 1.0 ? 1u : (uint32_t)keep);
+        d.seed_lo = (uint32_t)st->dropout_seed;
+        d.seed_hi = (uint32_t)(st->dropout_seed >> 32);
+        d.counter = st->dropout_counter++;
+    }
+    return d;
+}
+
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline size_t align_up(size_t a, size_t b) { return (a + b - 1) / b * b; }
 
@@ -252,9 +292,13 @@ dl4s_status decode_static_prepare(DeviceState *st);
 
 // gemm_f32.cu — C = alpha*op(A)op(B) + beta*C with a fused epilogue.
 enum Epilogue { EPI_NONE = 0, EPI_BIAS = 1, EPI_BIAS_GELU = 2, EPI_BIAS_RELU = 3, EPI_BIAS_RESIDUAL = 4, EPI_RESIDUAL = 5 };
+// `drop`: dropout of the product (+ bias) before the residual is added, for the residual flavours.
 dl4s_status launch_gemm_f32(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N,
                             int64_t K, float alpha, float beta, int trans_a, int trans_b, int epilogue,
-                            const float *bias, const float *residual);
+                            const float *bias, const float *residual, const DropoutSpec *drop = nullptr);
+
+// fused.cu: the sinusoidal positional-encoding table of the device covers at least `rows` positions of width D.
+dl4s_status ensure_positional_table(DeviceState *st, int64_t rows, int64_t D);
 
 // layernorm.cu
 dl4s_status launch_layernorm(DeviceState *st, const float *x, const float *residual, int64_t outer,

@@ -244,13 +244,14 @@ static dl4s_status mha_tc_run(DeviceState *st, const float *xq, const float *xk,
     po.c = m.pr;
     // The Wo epilogue leaves the LayerNorm's partial sums when the block shape allows it: one pass less over pr.
     const int parts = gemm_tc_stats_per_row_block(D);
+    const DropoutSpec drop = next_dropout(st);   // MultiHeadAttention.swift:122
     if (layernorm_stats_usable(B, Sq, D, parts)) {
         po.ln_stats = st->ln_partials;
-        DL4S_TRY(launch_gemm_tc_h(st, m.heads_h, m.wo_h, B * Sq, D, Nv, EPI_RESIDUAL_STATS, nullptr, xq, po, 1, 0, split));
+        DL4S_TRY(launch_gemm_tc_h(st, m.heads_h, m.wo_h, B * Sq, D, Nv, EPI_RESIDUAL_STATS, nullptr, xq, po, 1, 0, split, &drop));
         ScopedGroup ln(st, "LayerNorm");
         return launch_layernorm_from_stats(st, m.pr, B, Sq, D, g, sh, out, out_h, st->ln_partials, parts);
     }
-    DL4S_TRY(launch_gemm_tc_h(st, m.heads_h, m.wo_h, B * Sq, D, Nv, EPI_RESIDUAL, nullptr, xq, po, 1, 0, split));
+    DL4S_TRY(launch_gemm_tc_h(st, m.heads_h, m.wo_h, B * Sq, D, Nv, EPI_RESIDUAL, nullptr, xq, po, 1, 0, split, &drop));
     ScopedGroup ln(st, "LayerNorm");
     return launch_layernorm(st, m.pr, nullptr, B, Sq, D, g, sh, out, out_h);
 }
@@ -297,7 +298,8 @@ static dl4s_status ffn_tc_run(DeviceState *st, const float *x, int64_t M, int64_
     oo.c = f.o;
     {
         ScopedGroup dense(st, "Dense");
-        DL4S_TRY(launch_gemm_tc_h(st, f.h_h, f.w2_h, M, D, F, EPI_BIAS_RESIDUAL, b2, x, oo, 1, 0, split));
+        const DropoutSpec drop = next_dropout(st);   // PointwiseFeedForward.swift:78
+        DL4S_TRY(launch_gemm_tc_h(st, f.h_h, f.w2_h, M, D, F, EPI_BIAS_RESIDUAL, b2, x, oo, 1, 0, split, &drop));
     }
     ScopedGroup ln(st, "LayerNorm");
     return launch_layernorm(st, f.o, nullptr, M, 1, D, g, sh, out, out_h);
@@ -386,12 +388,13 @@ dl4s_status mha_output_tc(DeviceState *st, const void *heads, int heads_half, co
     po.c = pr;
     // As in the whole layer: the epilogue leaves the LayerNorm's partial sums where the block shape allows it.
     const int parts = gemm_tc_stats_per_row_block(D);
+    const DropoutSpec drop = next_dropout(st);   // MultiHeadAttention.swift:122
     if (layernorm_stats_usable(B, S, D, parts)) {
         po.ln_stats = st->ln_partials;
-        DL4S_TRY(launch_gemm_tc_h(st, a, w, M, D, HDv, EPI_RESIDUAL_STATS, nullptr, residual, po, groups, group_stride, split));
+        DL4S_TRY(launch_gemm_tc_h(st, a, w, M, D, HDv, EPI_RESIDUAL_STATS, nullptr, residual, po, groups, group_stride, split, &drop));
         return launch_layernorm_from_stats(st, pr, B, S, D, g, sh, out, nullptr, st->ln_partials, parts);
     }
-    DL4S_TRY(launch_gemm_tc_h(st, a, w, M, D, HDv, EPI_RESIDUAL, nullptr, residual, po, groups, group_stride, split));
+    DL4S_TRY(launch_gemm_tc_h(st, a, w, M, D, HDv, EPI_RESIDUAL, nullptr, residual, po, groups, group_stride, split, &drop));
     return launch_layernorm(st, pr, nullptr, B, S, D, g, sh, out, nullptr);
 }
 

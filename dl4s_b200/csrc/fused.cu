@@ -33,7 +33,8 @@ __global__ void __launch_bounds__(256) k_positional_table(int64_t S, int64_t D, 
 // embeds as zeros.
 __global__ void __launch_bounds__(256) k_embed_positional(const int32_t *__restrict__ ids, int64_t BS, int64_t S, int64_t D,
                                                           const float *__restrict__ E, int64_t vocab, int32_t ignore_index,
-                                                          float scale, const float *__restrict__ pe, float *__restrict__ out)
+                                                          float scale, const float *__restrict__ pe, float *__restrict__ out,
+                                                          DropoutSpec drop)
 {
     const int64_t half = D / 2;
     for (int64_t row = blockIdx.x; row < BS; row += gridDim.x) {
@@ -46,7 +47,13 @@ __global__ void __launch_bounds__(256) k_embed_positional(const int32_t *__restr
         for (int64_t i = threadIdx.x; i < half; i += blockDim.x) {
             float2 ev = zero ? make_float2(0.f, 0.f) : e[i];
             float2 pv = p[i];
-            o[i] = make_float2(ev.x * scale + pv.x, ev.y * scale + pv.y);
+            float2 r = make_float2(ev.x * scale + pv.x, ev.y * scale + pv.y);
+            if (drop.threshold != 0) {   // dropout(embedded * sqrt(D) + positions), Transformer.swift:87
+                const uint64_t e = (uint64_t)(row * D + 2 * i);
+                r.x = dropout_keep(drop, e) ? r.x : 0.f;
+                r.y = dropout_keep(drop, e + 1) ? r.y : 0.f;
+            }
+            o[i] = r;
         }
     }
 }
@@ -83,6 +90,25 @@ static inline bool prec_known(int p) { return p == DL4S_PREC_FP32 || p == DL4S_P
 static inline bool prec_tc(int p) { return p == DL4S_PREC_F16 || p == DL4S_PREC_F16_SPLIT; }
 static inline int prec_split(int p) { return p == DL4S_PREC_F16_SPLIT ? 1 : 0; }
 
+// The sinusoidal table [rows, D] is built on first use and kept; it is rebuilt when D changes or more rows are needed.
+dl4s_status ensure_positional_table(DeviceState *st, int64_t rows, int64_t D)
+{
+    if (st->pe_dim == D && st->pe_rows >= rows) return DL4S_OK;
+    if (st->capturing)
+        return fail(DL4S_ERR_UNSUPPORTED, "the positional-encoding table has to be built: run the call once before capturing");
+    // the old table may still be in use by work queued on the stream
+    DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
+    DL4S_TRY(release_internal(st, st->pe_table));
+    st->pe_table = nullptr;
+    st->pe_rows = 0;
+    DL4S_CUDA_TRY(cudaMalloc((void **)&st->pe_table, (size_t)(rows * D) * sizeof(float)));
+    st->pe_rows = rows;
+    st->pe_dim = D;
+    int64_t tb = rows < (int64_t)st->sm_count * 8 ? rows : (int64_t)st->sm_count * 8;
+    k_positional_table<<<(unsigned)tb, 256, 0, st->stream>>>(rows, D, st->pe_table);
+    return after_launch(st, "k_positional_table");
+}
+
 static dl4s_status check_mask(const MaskSpec &m, int64_t B, int64_t H, int64_t Sq, int64_t Sk)
 {
     if (!m.d_mask) return DL4S_OK;
@@ -117,11 +143,12 @@ static dl4s_status attention(DeviceState *st, const float *q, Strides4 qs, const
 }
 
 static dl4s_status gemm(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K, int epi,
-                        const float *bias, const float *residual, int precision, void *scratch, size_t scratch_bytes)
+                        const float *bias, const float *residual, int precision, void *scratch, size_t scratch_bytes,
+                        const DropoutSpec *drop = nullptr)
 {
     if (prec_tc(precision) && gemm_tc_supported(M, N, K))
-        return launch_gemm_tc(st, a, b, c, M, N, K, epi, bias, residual, scratch, scratch_bytes, prec_split(precision));
-    return launch_gemm_f32(st, a, b, c, M, N, K, 1.0f, 0.0f, 0, 0, epi, bias, residual);
+        return launch_gemm_tc(st, a, b, c, M, N, K, epi, bias, residual, scratch, scratch_bytes, prec_split(precision), drop);
+    return launch_gemm_f32(st, a, b, c, M, N, K, 1.0f, 0.0f, 0, 0, epi, bias, residual, drop);
 }
 
 struct MhaShape {
@@ -167,7 +194,8 @@ static dl4s_status mha_output(DeviceState *st, const float *heads, const float *
                               int64_t HDv, const float *wo, const float *g, const float *sh, float *out, int precision,
                               float *pr, void *extra, size_t extra_bytes)
 {
-    DL4S_TRY(gemm(st, heads, wo, pr, B * Sq, D, HDv, EPI_RESIDUAL, nullptr, residual, precision, extra, extra_bytes));
+    const DropoutSpec drop = next_dropout(st);   // MultiHeadAttention.swift:122
+    DL4S_TRY(gemm(st, heads, wo, pr, B * Sq, D, HDv, EPI_RESIDUAL, nullptr, residual, precision, extra, extra_bytes, &drop));
     return launch_layernorm(st, pr, nullptr, B, Sq, D, g, sh, out);
 }
 
@@ -195,7 +223,8 @@ static dl4s_status ffn(DeviceState *st, const float *x, int64_t M, int64_t D, in
     float *obuf = hbuf + M * F;
     int epi1 = act == DL4S_ACT_RELU ? EPI_BIAS_RELU : EPI_BIAS_GELU;
     DL4S_TRY(gemm(st, x, w1, hbuf, M, F, D, epi1, b1, nullptr, precision, extra, extra_bytes));
-    DL4S_TRY(gemm(st, hbuf, w2, obuf, M, D, F, EPI_BIAS_RESIDUAL, b2, x, precision, extra, extra_bytes));
+    const DropoutSpec drop = next_dropout(st);   // PointwiseFeedForward.swift:78
+    DL4S_TRY(gemm(st, hbuf, w2, obuf, M, D, F, EPI_BIAS_RESIDUAL, b2, x, precision, extra, extra_bytes, &drop));
     return launch_layernorm(st, obuf, nullptr, M, 1, D, g, sh, out);
 }
 
@@ -546,25 +575,11 @@ dl4s_status dl4s_cuda_embed_positional(const int32_t *d_ids, int64_t B, int64_t 
     DL4S_REQUIRE(B >= 0 && S >= 0 && D >= 2 && D % 2 == 0 && vocab >= 1, "bad extents (D must be even)");
     if (B * S == 0) return DL4S_OK;
     DL4S_REQUIRE((((uintptr_t)d_embedding | (uintptr_t)d_out) & 7) == 0, "embedding and output must be 8-byte aligned");
-    if (st->pe_dim != D || st->pe_rows < S) {
-        if (st->capturing)
-            return fail(DL4S_ERR_UNSUPPORTED, "the positional-encoding table has to be built: run the call once before capturing");
-        // (re)build the table; the old one may still be in use by work queued on the stream
-        DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
-        DL4S_TRY(release_internal(st, st->pe_table));
-        st->pe_table = nullptr;
-        st->pe_rows = 0;
-        DL4S_CUDA_TRY(cudaMalloc((void **)&st->pe_table, (size_t)(S * D) * sizeof(float)));
-        st->pe_rows = S;
-        st->pe_dim = D;
-        int64_t tb = S < (int64_t)st->sm_count * 8 ? S : (int64_t)st->sm_count * 8;
-        k_positional_table<<<(unsigned)tb, 256, 0, st->stream>>>(S, D, st->pe_table);
-        DL4S_TRY(after_launch(st, "k_positional_table"));
-    }
+    DL4S_TRY(ensure_positional_table(st, S, D));
     ScopedGroup group(st, "Embedding");
     int64_t blocks = B * S < (int64_t)st->sm_count * 16 ? B * S : (int64_t)st->sm_count * 16;
     k_embed_positional<<<(unsigned)blocks, 256, 0, st->stream>>>(d_ids, B * S, S, D, d_embedding, vocab, ignore_index,
-                                                                sqrtf((float)D), st->pe_table, d_out);
+                                                                sqrtf((float)D), st->pe_table, d_out, next_dropout(st));
     return after_launch(st, "k_embed_positional");
 }
 

@@ -26,7 +26,7 @@ template <bool TA, bool TB>
 __global__ void __launch_bounds__(GT) k_gemm_f32(const float *__restrict__ A, const float *__restrict__ B,
                                                  float *__restrict__ C, int64_t M, int64_t N, int64_t K, float alpha,
                                                  float beta, int epilogue, const float *__restrict__ bias,
-                                                 const float *__restrict__ residual)
+                                                 const float *__restrict__ residual, DropoutSpec drop)
 {
     __shared__ __align__(16) float As[2][BK][BM + 4];
     __shared__ __align__(16) float Bs[2][BK][BN + 4];
@@ -143,8 +143,11 @@ __global__ void __launch_bounds__(GT) k_gemm_f32(const float *__restrict__ A, co
                 case EPI_BIAS: v = v + bias[gn]; break;
                 case EPI_BIAS_GELU: v = gelu_sigmoid(v + bias[gn]); break;
                 case EPI_BIAS_RELU: v = v + bias[gn]; v = v > 0.f ? v : 0.f; break;
-                case EPI_BIAS_RESIDUAL: v = (v + bias[gn]) + residual[gm * N + gn]; break;
-                case EPI_RESIDUAL: v = v + residual[gm * N + gn]; break;
+                case EPI_BIAS_RESIDUAL:
+                    v = v + bias[gn];
+                    v = (dropout_keep(drop, (uint64_t)(gm * N + gn)) ? v : 0.f) + residual[gm * N + gn];
+                    break;
+                case EPI_RESIDUAL: v = (dropout_keep(drop, (uint64_t)(gm * N + gn)) ? v : 0.f) + residual[gm * N + gn]; break;
                 default: break;
             }
             C[gm * N + gn] = v;
@@ -320,7 +323,7 @@ __global__ void __launch_bounds__(ST_THREADS) k_gemm_skinny_tiled(const float *_
 
 __global__ void __launch_bounds__(256) k_gemm_skinny_reduce(const float *__restrict__ P, int splits, int64_t MN, int64_t N,
                                                             int epilogue, const float *__restrict__ bias,
-                                                            const float *__restrict__ residual, float *__restrict__ C)
+                                                            const float *__restrict__ residual, float *__restrict__ C, DropoutSpec drop)
 {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < MN; i += (int64_t)gridDim.x * blockDim.x) {
         float v = 0.f;
@@ -330,8 +333,11 @@ __global__ void __launch_bounds__(256) k_gemm_skinny_reduce(const float *__restr
             case EPI_BIAS: v = v + bias[gn]; break;
             case EPI_BIAS_GELU: v = gelu_sigmoid(v + bias[gn]); break;
             case EPI_BIAS_RELU: v = v + bias[gn]; v = v > 0.f ? v : 0.f; break;
-            case EPI_BIAS_RESIDUAL: v = (v + bias[gn]) + residual[i]; break;
-            case EPI_RESIDUAL: v = v + residual[i]; break;
+            case EPI_BIAS_RESIDUAL:
+                v = v + bias[gn];
+                v = (dropout_keep(drop, (uint64_t)i) ? v : 0.f) + residual[i];
+                break;
+            case EPI_RESIDUAL: v = (dropout_keep(drop, (uint64_t)i) ? v : 0.f) + residual[i]; break;
             default: break;
         }
         C[i] = v;
@@ -339,7 +345,7 @@ __global__ void __launch_bounds__(256) k_gemm_skinny_reduce(const float *__restr
 }
 
 static dl4s_status launch_gemm_skinny(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K,
-                                      int epilogue, const float *bias, const float *residual)
+                                      int epilogue, const float *bias, const float *residual, DropoutSpec drop)
 {
     // Two CTAs of this kernel fit an SM; K is split so that all CTAs are resident at once (a second, nearly
     // empty wave would double the time).
@@ -369,23 +375,24 @@ static dl4s_status launch_gemm_skinny(DeviceState *st, const float *a, const flo
     DL4S_TRY(after_launch(st, "k_gemm_skinny_f32"));
     int64_t blocks = ceil_div(M * N, 256);
     if (blocks > (int64_t)st->sm_count * 8) blocks = (int64_t)st->sm_count * 8;
-    k_gemm_skinny_reduce<<<(unsigned)blocks, 256, 0, st->stream>>>(P, (int)splits, M * N, N, epilogue, bias, residual, c);
+    k_gemm_skinny_reduce<<<(unsigned)blocks, 256, 0, st->stream>>>(P, (int)splits, M * N, N, epilogue, bias, residual, c, drop);
     return after_launch(st, "k_gemm_skinny_reduce");
 }
 
 dl4s_status launch_gemm_f32(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K,
                             float alpha, float beta, int trans_a, int trans_b, int epilogue, const float *bias,
-                            const float *residual)
+                            const float *residual, const DropoutSpec *dropp)
 {
     if (M == 0 || N == 0) return DL4S_OK;
+    const DropoutSpec drop = dropp ? *dropp : DropoutSpec();
     if (!trans_a && !trans_b && M <= 64 && N >= 512 && K >= 512 && alpha == 1.0f && beta == 0.0f && splits_fit(M, N))
-        return launch_gemm_skinny(st, a, b, c, M, N, K, epilogue, bias, residual);
+        return launch_gemm_skinny(st, a, b, c, M, N, K, epilogue, bias, residual, drop);
     dim3 grid((unsigned)ceil_div(N, BN), (unsigned)ceil_div(M, BM));
     DL4S_REQUIRE(ceil_div(M, BM) <= 65535, "M too large for the fp32 gemm grid");
-    if (!trans_a && !trans_b) k_gemm_f32<false, false><<<grid, GT, 0, st->stream>>>(a, b, c, M, N, K, alpha, beta, epilogue, bias, residual);
-    else if (!trans_a && trans_b) k_gemm_f32<false, true><<<grid, GT, 0, st->stream>>>(a, b, c, M, N, K, alpha, beta, epilogue, bias, residual);
-    else if (trans_a && !trans_b) k_gemm_f32<true, false><<<grid, GT, 0, st->stream>>>(a, b, c, M, N, K, alpha, beta, epilogue, bias, residual);
-    else k_gemm_f32<true, true><<<grid, GT, 0, st->stream>>>(a, b, c, M, N, K, alpha, beta, epilogue, bias, residual);
+    if (!trans_a && !trans_b) k_gemm_f32<false, false><<<grid, GT, 0, st->stream>>>(a, b, c, M, N, K, alpha, beta, epilogue, bias, residual, drop);
+    else if (!trans_a && trans_b) k_gemm_f32<false, true><<<grid, GT, 0, st->stream>>>(a, b, c, M, N, K, alpha, beta, epilogue, bias, residual, drop);
+    else if (trans_a && !trans_b) k_gemm_f32<true, false><<<grid, GT, 0, st->stream>>>(a, b, c, M, N, K, alpha, beta, epilogue, bias, residual, drop);
+    else k_gemm_f32<true, true><<<grid, GT, 0, st->stream>>>(a, b, c, M, N, K, alpha, beta, epilogue, bias, residual, drop);
     return after_launch(st, "k_gemm_f32");
 }
 

@@ -158,6 +158,7 @@ struct GemmTcParams {
     double *ln_stats;        // EPI_RESIDUAL_STATS: partial sums per (32 rows, half tile), see tc.cuh
     int32_t *tile_counter;   // {tiles handed out beyond the first gridDim.x, CTAs done}
     int a_kc;                // A's k extent per column group (K when A is one plain matrix)
+    DropoutSpec drop;        // residual flavours: dropout of the product (+ bias) before the residual is added
     int test_skip_kb;        // -1; test only: the k-block of a CTA's first tile whose loads are left out
     uint32_t wait_polls;     // poll limit of every bounded wait (kWaitPolls; short under an injected fault)
     int a_groups;            // column groups of A; the k walk wraps to group 0 after the last one (split B: K = 2 x A's width)
@@ -501,6 +502,13 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                                 break;
                             default: break;
                         }
+                        if (kHasResidual && p.drop.threshold != 0) {
+                            // Dropout.swift:47-55 on the projection's output (MultiHeadAttention.swift:122,
+                            // PointwiseFeedForward.swift:78): element (row, column) of the [M, N] result
+                            const uint64_t e = (uint64_t)((first_row + rq * 8) * p.N + col0 + cg + pp * 8);
+                            t.x = dropout_keep(p.drop, e) ? t.x : 0.f;
+                            t.y = dropout_keep(p.drop, e + 1) ? t.y : 0.f;
+                        }
                         if (kHasResidual) {
                             const float2 q = kPrefetchResidual ? res[kPrefetchResidual ? rq * 4 + pp : 0]
                                              : row_ok      ? *reinterpret_cast<const float2 *>(rp + (int64_t)rq * 8 * p.N + pp * 8)
@@ -741,7 +749,7 @@ static dl4s_status run_gemm_tc(DeviceState *st, const CUtensorMap &ta, const CUt
 
 dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_half, int64_t M, int64_t N, int64_t K,
                              int epilogue, const float *bias, const float *residual, const GemmTcOut &out,
-                             int64_t a_groups, int64_t a_group_stride, int b_split)
+                             int64_t a_groups, int64_t a_group_stride, int b_split, const DropoutSpec *drop)
 {
     DL4S_REQUIRE(gemm_tc_supported(M, N, K), "shape not supported by the tensor-core gemm");
     DL4S_REQUIRE(2 * K < (1ll << 31), "K too large");
@@ -764,6 +772,8 @@ dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_
     p.M = M; p.N = N; p.K = Kb;
     p.a_kc = (int)kc;
     p.a_groups = (int)a_groups;
+    p.drop = drop ? *drop : DropoutSpec();
+    DL4S_REQUIRE(p.drop.threshold == 0 || epi_has_residual(epilogue), "dropout is fused into the residual epilogues only");
     p.ln_stats = out.ln_stats;
     DL4S_REQUIRE(epilogue != EPI_RESIDUAL_STATS || (out.ln_stats && out.mode == OUT_F32), "the statistics epilogue needs its buffer");
     p.epilogue = epilogue;
@@ -798,7 +808,8 @@ dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_
 }
 
 dl4s_status launch_gemm_tc(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K,
-                           int epilogue, const float *bias, const float *residual, void *scratch, size_t scratch_bytes, int split)
+                           int epilogue, const float *bias, const float *residual, void *scratch, size_t scratch_bytes, int split,
+                           const DropoutSpec *drop)
 {
     DL4S_REQUIRE(gemm_tc_supported(M, N, K), "shape not supported by the tensor-core gemm");
     DL4S_REQUIRE(scratch && scratch_bytes >= gemm_tc_scratch_bytes(M, N, K, split), "scratch too small");
@@ -811,7 +822,7 @@ dl4s_status launch_gemm_tc(DeviceState *st, const float *a, const float *b, floa
     GemmTcOut out;
     out.mode = OUT_F32;
     out.c = c;
-    return launch_gemm_tc_h(st, ah, bh, M, N, K, epilogue, bias, residual, out, 1, 0, split);
+    return launch_gemm_tc_h(st, ah, bh, M, N, K, epilogue, bias, residual, out, 1, 0, split, drop);
 }
 
 }  // namespace dl4s

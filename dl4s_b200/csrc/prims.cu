@@ -329,6 +329,14 @@ __global__ void __launch_bounds__(kThreads) k_band(const float *__restrict__ x, 
     }
 }
 
+// y = x * bernoulli(1 - rate) with the counter-based mask of common.cuh (Dropout.swift:47-55).
+__global__ void __launch_bounds__(kThreads) k_dropout(const float *__restrict__ x, float *__restrict__ y, int64_t n, DropoutSpec drop)
+{
+    int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = tid; i < n; i += stride) y[i] = dropout_keep(drop, (uint64_t)i) ? x[i] : 0.f;
+}
+
 // result[o, j] = stacked[o * row + j] + add[o, j] for the slab of `inner` columns that starts at `stacked`.
 __global__ void __launch_bounds__(kThreads) k_unstack_add(const float *__restrict__ stacked, int64_t row, const float *__restrict__ add,
                                                           float *__restrict__ y, int64_t outer, int64_t inner)
@@ -534,6 +542,41 @@ dl4s_status dl4s_cuda_unstack_add(const float *d_stacked, const float *const *d_
 {
     DL4S_REQUIRE(d_add, "add is NULL");
     return unstack_impl(d_stacked, d_add, d_results, shapes, n, dim, axis);
+}
+
+dl4s_status dl4s_cuda_set_dropout(float rate, uint64_t seed)
+{
+    DL4S_STATE(st);
+    DL4S_REQUIRE(rate >= 0.f && rate < 1.f, "the dropout rate must lie in [0, 1) (got %g)", (double)rate);
+    st->dropout_rate = rate;
+    st->dropout_seed = seed;
+    return DL4S_OK;
+}
+
+dl4s_status dl4s_cuda_dropout_counter(uint32_t *current, const uint32_t *set_to)
+{
+    DL4S_STATE(st);
+    if (set_to) st->dropout_counter = *set_to;
+    if (current) *current = st->dropout_counter;
+    return DL4S_OK;
+}
+
+dl4s_status dl4s_cuda_dropout(const float *d_x, float *d_result, int64_t count, float rate, uint64_t seed, uint32_t counter)
+{
+    DL4S_STATE(st);
+    DL4S_REQUIRE(count >= 0 && (count == 0 || (d_x && d_result)), "bad arguments");
+    DL4S_REQUIRE(rate >= 0.f && rate < 1.f, "the dropout rate must lie in [0, 1) (got %g)", (double)rate);
+    if (count == 0) return DL4S_OK;
+    DropoutSpec d;
+    if (rate > 0.f) {
+        double keep = (1.0 - (double)rate) * 4294967296.0;
+        d.threshold = keep >= 4294967295.0 ? 0xFFFFFFFFu : (keep < 1.0 ? 1u : (uint32_t)keep);
+        d.seed_lo = (uint32_t)seed;
+        d.seed_hi = (uint32_t)(seed >> 32);
+        d.counter = counter;
+    }
+    k_dropout<<<grid_for(st, count, kThreads * 2), kThreads, 0, st->stream>>>(d_x, d_result, count, d);
+    return after_launch(st, "k_dropout");
 }
 
 dl4s_status dl4s_cuda_band(const float *d_src, int64_t rows, int64_t cols, int32_t below, int32_t has_below, int32_t above,

@@ -12,7 +12,7 @@ bool gemm_tc_supported(int64_t M, int64_t N, int64_t K);
 size_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int split = 0);
 dl4s_status launch_gemm_tc(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K,
                            int epilogue, const float *bias, const float *residual, void *scratch, size_t scratch_bytes,
-                           int split = 0);
+                           int split = 0, const DropoutSpec *drop = nullptr);
 
 // The same product with operands that are already half ([M,K] and [K,N], 16-byte aligned)
 // and a choice of output: fp32 [M,N], half [M,N], or half scattered head-major into up to
@@ -42,7 +42,8 @@ int gemm_tc_stats_per_row_block(int64_t N);
 // a_half[g * a_group_stride + m * K/a_groups + c] (the rank-major layout of an all-gather).
 dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_half, int64_t M, int64_t N, int64_t K,
                              int epilogue, const float *bias, const float *residual, const GemmTcOut &out,
-                             int64_t a_groups = 1, int64_t a_group_stride = 0, int b_split = 0);
+                             int64_t a_groups = 1, int64_t a_group_stride = 0, int b_split = 0,
+                             const DropoutSpec *drop = nullptr);
 dl4s_status launch_f32_to_f16(DeviceState *st, const float *x, void *y, int64_t n);
 // hi = half(x), lo = half(x - hi): the two-half form of a weight matrix (b_split above reads [hi; lo] stacked along k).
 dl4s_status launch_f32_to_f16_hilo(DeviceState *st, const float *x, void *hi, void *lo, int64_t n);

@@ -43,6 +43,43 @@ class LayerNorm:
         return out
 
 
+class Dropout:
+    """NN/Layer/Dropout.swift:29-57: inputs * bernoulli(1 - rate) while `isActive`, without rescaling. The mask is a
+    counter-based hash on the device (include/dl4s_cuda.h); `seed` and the device's dropout counter determine it."""
+
+    def __init__(self, rate: float, seed: int = 0):
+        self.rate, self.seed, self.isActive = float(rate), int(seed), True
+
+    parameters: list = []
+
+    def __call__(self, inputs: ShapedBuffer) -> ShapedBuffer:
+        if not self.isActive or self.rate == 0.0:
+            return inputs
+        out = CUDA.Memory.allocateBuffer(inputs.shape)
+        cur = ctypes.c_uint32(0)
+        call("dl4s_cuda_dropout_counter", ctypes.byref(cur), None)
+        nxt = ctypes.c_uint32(cur.value + 1)
+        call("dl4s_cuda_dropout_counter", None, ctypes.byref(nxt))
+        call("dl4s_cuda_dropout", c_vp(inputs.ptr), c_vp(out.ptr), inputs.count, c_f32(self.rate), self.seed, cur.value)
+        return out
+
+
+def setDropout(rate: float, seed: int = 0) -> None:
+    """Rate and seed of the dropout fused into MultiHeadAttention, PointwiseFeedForward and the input embedding on the
+    current device (the `dropout` arguments of the reference's initialisers); 0 turns it off."""
+    call("dl4s_cuda_set_dropout", c_f32(rate), int(seed))
+
+
+def dropoutCounter(set_to: Optional[int] = None) -> int:
+    cur = ctypes.c_uint32(0)
+    if set_to is None:
+        call("dl4s_cuda_dropout_counter", ctypes.byref(cur), None)
+    else:
+        v = ctypes.c_uint32(set_to)
+        call("dl4s_cuda_dropout_counter", ctypes.byref(cur), ctypes.byref(v))
+    return cur.value
+
+
 class ScaledDotProductAttention:
     """NN/Models/Transformer/ScaledDotProductAttention.swift:29-64."""
 
@@ -344,3 +381,133 @@ class OutputHead:
         call("dl4s_cuda_output_head", c_vp(decoded.ptr), M, D, c_vp(self.embedding.embeddingMatrix.ptr), V,
              c_vp(self.outputBias.ptr), c_vp(out.ptr), prec)
         return out
+
+
+DECODER_PARAM_ORDER = ("self_Wq", "self_Wk", "self_Wv", "self_Wo", "self_ln_scale", "self_ln_shift",
+                       "enc_Wq", "enc_Wk", "enc_Wv", "enc_Wo", "enc_ln_scale", "enc_ln_shift",
+                       "W1", "b1", "W2", "b2", "ln_scale", "ln_shift")
+
+
+def decoder_layer_weights(rng: np.random.Generator, D: int, H: int, dk: int, dv: int, F: int) -> dict:
+    """One decoder block's parameters in the order the C ABI packs them (TransformerDecoderBlock.parameters)."""
+    w = {}
+    for pre in ("self", "enc"):
+        w[f"{pre}_Wq"] = xavier_uniform(rng, D, H * dk)
+        w[f"{pre}_Wk"] = xavier_uniform(rng, D, H * dk)
+        w[f"{pre}_Wv"] = xavier_uniform(rng, D, H * dv)
+        w[f"{pre}_Wo"] = xavier_uniform(rng, H * dv, D)
+        w[f"{pre}_ln_scale"] = np.ones(D, np.float32)
+        w[f"{pre}_ln_shift"] = np.zeros(D, np.float32)
+    w.update({"W1": xavier_uniform(rng, D, F), "b1": np.zeros(F, np.float32), "W2": xavier_uniform(rng, F, D),
+              "b2": np.zeros(D, np.float32), "ln_scale": np.ones(D, np.float32), "ln_shift": np.zeros(D, np.float32)})
+    return w
+
+
+class TransformerDecoder:
+    """NN/Models/Transformer/TransformerDecoder.swift:29-62 with TransformerDecoderBlock.swift:29-68. `__call__` runs
+    the whole stack in one library call (dl4s_cuda_decoder_forward); `makeCache` / `step` decode incrementally."""
+
+    def __init__(self, layerCount: int, heads: int, keyDim: int, valueDim: int, modelDim: int, forwardDim: int,
+                 rng: Optional[np.random.Generator] = None, layers: Optional[list] = None,
+                 activation: int = _lib.ACT_GELU_SIGMOID, precision: Optional[int] = None):
+        rng = rng or np.random.default_rng(0)
+        self.layerCount, self.heads, self.keyDim, self.valueDim = layerCount, heads, keyDim, valueDim
+        self.modelDim, self.forwardDim, self.activation, self.precision = modelDim, forwardDim, activation, precision
+        self.host_layers = layers or [decoder_layer_weights(rng, modelDim, heads, keyDim, valueDim, forwardDim)
+                                      for _ in range(layerCount)]
+        flat = np.concatenate([np.ascontiguousarray(l[k], np.float32).ravel() for l in self.host_layers
+                               for k in DECODER_PARAM_ORDER]) if layerCount else np.zeros(1, np.float32)
+        self.params = tensor(flat)
+
+    def __call__(self, decoderInput: ShapedBuffer, encoderStates: ShapedBuffer, encoderInputLengths=None,
+                 decoderInputLengths=None, out: Optional[ShapedBuffer] = None) -> ShapedBuffer:
+        B, St, D = decoderInput.shape
+        Ss = encoderStates.shape[1]
+        el = None if encoderInputLengths is None else tensor(np.asarray(encoderInputLengths, np.int32), np.int32)
+        dl = None if decoderInputLengths is None else tensor(np.asarray(decoderInputLengths, np.int32), np.int32)
+        out = out or CUDA.Memory.allocateBuffer((B, St, D))
+        prec = CUDAEngine.precision if self.precision is None else self.precision
+        call("dl4s_cuda_decoder_forward", c_vp(decoderInput.ptr), c_vp(encoderStates.ptr), B, St, Ss, D, self.heads, self.keyDim,
+             self.valueDim, self.forwardDim, self.layerCount, c_vp(self.params.ptr), c_vp(dl.ptr if dl else 0),
+             c_vp(el.ptr if el else 0), self.activation, c_vp(out.ptr), prec)
+        return out
+
+    def makeCache(self, batch: int, maxLength: int, encoderStates: ShapedBuffer, encoderInputLengths=None) -> "DecoderCache":
+        return DecoderCache(self, batch, maxLength, encoderStates, encoderInputLengths)
+
+
+class DecoderCache:
+    """Per-layer self-attention key/value caches and the encoder keys/values projected once, for incremental
+    decoding with TransformerDecoder.step-wise calls (dl4s_cuda_decoder_cache_* / dl4s_cuda_decoder_step)."""
+
+    def __init__(self, decoder: TransformerDecoder, batch: int, maxLength: int, encoderStates: ShapedBuffer,
+                 encoderInputLengths=None):
+        self.decoder = decoder
+        self.batch = batch
+        d = decoder
+        self._h = c_vp(0)
+        call("dl4s_cuda_decoder_cache_create", batch, maxLength, encoderStates.shape[1], d.modelDim, d.heads, d.keyDim, d.valueDim,
+             d.forwardDim, d.layerCount, c_vp(d.params.ptr), ctypes.byref(self._h))
+        self.setEncoder(encoderStates, encoderInputLengths)
+
+    def setEncoder(self, encoderStates: ShapedBuffer, encoderInputLengths=None) -> None:
+        el = None if encoderInputLengths is None else tensor(np.asarray(encoderInputLengths, np.int32), np.int32)
+        call("dl4s_cuda_decoder_cache_set_encoder", self._h, c_vp(encoderStates.ptr), c_vp(el.ptr if el else 0))
+
+    def step(self, x: ShapedBuffer, out: Optional[ShapedBuffer] = None) -> ShapedBuffer:
+        """x [B, D]: the current token's embedded input per sequence -> the decoder's output row per sequence."""
+        out = out or CUDA.Memory.allocateBuffer(x.shape)
+        call("dl4s_cuda_decoder_step", self._h, c_vp(x.ptr), self.decoder.activation, c_vp(out.ptr))
+        return out
+
+    def destroy(self) -> None:
+        if self._h:
+            call("dl4s_cuda_decoder_cache_destroy", self._h)
+            self._h = c_vp(0)
+
+    def __del__(self):
+        try:
+            if self._h:
+                _lib.load().dl4s_cuda_decoder_cache_destroy(self._h)
+        except Exception:
+            pass
+
+
+class Transformer:
+    """NN/Models/Transformer/Transformer.swift:29-137: shared embedding, encoder, decoder, tied output head.
+    `__call__` is the teacher-forced forward (:96-108); `greedyDecode` is callAsFunction(inputSequence:...) (:118-137)."""
+
+    def __init__(self, encoderLayers: int, decoderLayers: int, vocabSize: int, hiddenDim: int, heads: int, keyDim: int,
+                 valueDim: int, forwardDim: int, rng: Optional[np.random.Generator] = None, weights: Optional[dict] = None,
+                 precision: Optional[int] = None):
+        rng = rng or np.random.default_rng(0)
+        w = weights or {}
+        E = w.get("embedding")
+        if E is None:
+            E = (rng.standard_normal((vocabSize, hiddenDim)) * 0.02).astype(np.float32)
+        self.vocabSize, self.hiddenDim, self.precision = vocabSize, hiddenDim, precision
+        self.embedding = EmbeddingWithPositions(E, ignoreIndex=-1)
+        self.encoder = TransformerEncoder(encoderLayers, heads, keyDim, valueDim, hiddenDim, forwardDim, rng=rng,
+                                          layers=w.get("encoder"), precision=precision)
+        self.decoder = TransformerDecoder(decoderLayers, heads, keyDim, valueDim, hiddenDim, forwardDim, rng=rng,
+                                          layers=w.get("decoder"), precision=precision)
+        self.head = OutputHead(self.embedding, w.get("outputBias"), precision=precision)
+
+    def __call__(self, encoderInput: np.ndarray, decoderInput: np.ndarray, encoderInputLengths, decoderInputLengths) -> ShapedBuffer:
+        enc_in = self.embedding(tensor(encoderInput, np.int32))
+        dec_in = self.embedding(tensor(decoderInput, np.int32))
+        states = self.encoder(enc_in, np.asarray(encoderInputLengths, np.int32))
+        decoded = self.decoder(dec_in, states, encoderInputLengths, decoderInputLengths)
+        return self.head(decoded)
+
+    def greedyDecode(self, inputSequence, startToken: int, endToken: int, maxLength: int, cached: bool = False):
+        ids = np.ascontiguousarray(inputSequence, np.int32)
+        toks = np.zeros(maxLength, np.int32)
+        n = ctypes.c_int64(0)
+        e, d = self.encoder, self.decoder
+        prec = CUDAEngine.precision if self.precision is None else self.precision
+        call("dl4s_cuda_transformer_greedy_decode", ids.ctypes.data_as(_lib.c_i32p), len(ids), startToken, endToken, maxLength,
+             self.vocabSize, self.hiddenDim, e.heads, e.keyDim, e.valueDim, e.forwardDim, e.layerCount, d.layerCount,
+             c_vp(self.embedding.embeddingMatrix.ptr), c_vp(e.params.ptr), c_vp(d.params.ptr), e.activation, prec, int(cached),
+             toks.ctypes.data_as(_lib.c_i32p), ctypes.byref(n))
+        return toks[:n.value].tolist()

@@ -232,6 +232,28 @@ dl4s_status dl4s_cuda_band(const float *d_src, int64_t rows, int64_t cols, int32
 dl4s_status dl4s_cuda_gemm(const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
                            float alpha, float beta, int32_t trans_a, int32_t trans_b, int32_t precision);
 
+/* Dropout (NN/Layer/Dropout.swift:47-55): y = x * bernoulli(1 - rate), NOT rescaled by 1/(1 - rate). DL4S draws the
+ * mask on the host from a process-global generator (Random.swift:148-157) and copies it to the device per call; here
+ * the mask is a counter-based hash evaluated where the value is produced. Element i of dropout site `counter` is
+ * kept when hash32(seed, counter, i) < floor((1 - rate) * 2^32), with
+ *   h = (uint32)i * 0x9E3779B1 + (uint32)seed;  h ^= h >> 16; h *= 0x85EBCA6B; h ^= h >> 13; h *= 0xC2B2AE35; h ^= h >> 16;
+ *   h += (((uint32)(i >> 32)) ^ counter) * 0x27D4EB2F + (uint32)(seed >> 32);
+ *   h ^= h >> 15; h *= 0x2C1B3C6D; h ^= h >> 12; h *= 0x297A2D39; h ^= h >> 15;
+ * in 32-bit wrap-around arithmetic, so a host can regenerate any mask (the parity tests do).
+ *   dropout          the layer itself on a buffer of `count` elements.
+ *   set_dropout      rate and seed of the dropout fused into the layer calls of the current device: the output
+ *                    projection of MultiHeadAttention (MultiHeadAttention.swift:122), the second Dense of
+ *                    PointwiseFeedForward (PointwiseFeedForward.swift:78) and the embedded inputs
+ *                    (Transformer.swift:87), each inside the kernel that produces the values (element index = the
+ *                    row-major index in that [rows, D] result). rate 0 (the default) turns it off; the decoding
+ *                    steps never apply it (inference).
+ *   dropout_counter  every site that applies dropout takes the next counter value (in call order: per encoder layer
+ *                    first the attention site, then the feed-forward site); reads it, and sets it when set_to is not
+ *                    NULL. A recorded graph replays the counters it was recorded with. */
+dl4s_status dl4s_cuda_dropout(const float *d_x, float *d_result, int64_t count, float rate, uint64_t seed, uint32_t counter);
+dl4s_status dl4s_cuda_set_dropout(float rate, uint64_t seed);
+dl4s_status dl4s_cuda_dropout_counter(uint32_t *current, const uint32_t *set_to);
+
 /* ------------------------------------------------------------- fused hot path */
 
 /* ScaledDotProductAttention.callAsFunction
@@ -411,6 +433,66 @@ dl4s_status dl4s_cuda_mha_decode_step(const float *d_x, int64_t B, int64_t D, in
                                       const float *d_ln_scale, const float *d_ln_shift,
                                       float *d_k_cache, float *d_v_cache, int64_t Lmax,
                                       const int32_t *d_lengths, float *d_out);
+
+/* TransformerDecoder.callAsFunction (NN/Models/Transformer/TransformerDecoder.swift:49-62) over whole sequences:
+ * `layers` blocks of TransformerDecoderBlock.callAsFunction (TransformerDecoderBlock.swift:61-68),
+ *   decAttn = MHA(x, x, x, decoderMask); encAttn = MHA(decAttn, enc, enc, encoderMask); x' = FFN(encAttn),
+ * with decoderMask = causal OR padding by d_dec_lengths[B] and encoderMask = padding by d_enc_lengths[B]
+ * (makeDecoderMasks / makeEncoderMasks, TransformerUtil.swift:29-50; either pointer may be NULL: no padding).
+ * d_x [B,St,D] decoder input, d_enc [B,Ss,D] encoder states. d_params holds, per layer and in the order of
+ * TransformerDecoderBlock.parameters: self-attention Wq, Wk [D,H*dk], Wv [D,H*dv], Wo [H*dv,D], ln_scale, ln_shift
+ * [D]; encoder attention the same six; W1 [D,F], b1 [F], W2 [F,D], b2 [D], ln_scale, ln_shift [D]. */
+dl4s_status dl4s_cuda_decoder_forward(const float *d_x, const float *d_enc, int64_t B, int64_t St, int64_t Ss, int64_t D,
+                                      int64_t H, int64_t dk, int64_t dv, int64_t F, int64_t layers, const float *d_params,
+                                      const int32_t *d_dec_lengths, const int32_t *d_enc_lengths, int32_t act,
+                                      float *d_out, int32_t precision);
+
+/* Incremental decoding through a whole decoder stack (no counterpart in DL4S, which re-runs the decoder on the
+ * growing prefix for every token, Transformer.swift:122-134). The cache holds, per layer, the self-attention keys
+ * and values of the tokens decoded so far [B,H,Lmax,d] and the encoder keys and values, projected ONCE per input
+ * sequence [B,H,Ss,d] (they do not change while a sequence is decoded).
+ *   mha_kv_project     k = x Wk, v = x Wv for x [B,S,D], written head-major into caches [B,H,Lmax,d] (rows 0..S-1):
+ *                      the projection half of MultiHeadAttention.swift:110-115 for keys and values.
+ *   cache_create       allocates the caches for B sequences, Lmax decoded tokens and Ss encoder positions; d_params
+ *                      (layout of dl4s_cuda_decoder_forward) must stay valid while the cache lives.
+ *   cache_set_encoder  projects d_enc [B,Ss,D] through every layer's encoder-attention Wk / Wv and resets the
+ *                      decoded length to 0: the start of a new batch of sequences.
+ *   decoder_step       one token per sequence, d_x [B,D] -> d_out [B,D], through every layer: self-attention over
+ *                      the cache and the token (dl4s_cuda_mha_decode_step), encoder attention of the token's query
+ *                      over the projected encoder keys/values (the decode attention kernel), feed-forward; then the
+ *                      decoded length advances by one. fp32.
+ *   cache_lengths      device address of the decoded length per sequence [B] (int32), e.g. to rewind.
+ * Each token's LayerNorm runs over its own [1, D] block. DL4S's LayerNorm inside MultiHeadAttention normalises the
+ * whole [prefix, D] block of a sequence at once, so its statistics move every earlier row with every new token
+ * and NO cache can reproduce what the reference recomputes; dl4s_cuda_decoder_forward on the prefix does. */
+dl4s_status dl4s_cuda_mha_kv_project(const float *d_x, int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk, int64_t dv,
+                                     const float *d_wk, const float *d_wv, float *d_k_cache, float *d_v_cache, int64_t Lmax);
+dl4s_status dl4s_cuda_decoder_cache_create(int64_t B, int64_t Lmax, int64_t Ss, int64_t D, int64_t H, int64_t dk, int64_t dv,
+                                           int64_t F, int64_t layers, const float *d_params, void **cache);
+dl4s_status dl4s_cuda_decoder_cache_set_encoder(void *cache, const float *d_enc, const int32_t *d_enc_lengths);
+dl4s_status dl4s_cuda_decoder_cache_lengths(void *cache, int32_t **d_lengths);
+dl4s_status dl4s_cuda_decoder_step(void *cache, const float *d_x, int32_t act, float *d_out);
+dl4s_status dl4s_cuda_decoder_cache_destroy(void *cache);
+/* x[b,:] = E[ids[b * ids_stride]] * sqrt(D) + PE[position,:]: Transformer.prepareInputs (Transformer.swift:82-88)
+ * for the one token per sequence a decoding step feeds back; the ids stay on the device. */
+dl4s_status dl4s_cuda_embed_at(const int32_t *d_ids, int64_t ids_stride, int64_t B, int64_t position, int64_t D,
+                               const float *d_embedding, int64_t vocab, int32_t ignore_index, float *d_out);
+
+/* Transformer.callAsFunction(inputSequence:startToken:endToken:maxLength:) (Transformer.swift:118-137): greedy
+ * decoding of one sequence. input_ids (host, n_in tokens) go through embedding + positional encoding and the
+ * encoder; then, per step, the decoder's last row is multiplied with the tied embedding matrix (no bias, no
+ * softmax, as in :127-129) and the arg-max token is appended, until end_token or max_length tokens. The tokens stay
+ * on the device between steps (the host looks at them every 8 steps to stop early). tokens (host) must hold
+ * max_length entries; the end token, if produced, is the last one counted in *n_tokens, as in the reference.
+ *   cached = 0  the reference's schedule: the decoder is re-run on [start] + tokens for every step
+ *               (dl4s_cuda_decoder_forward; `precision` selects its arithmetic). Token-for-token what DL4S computes.
+ *   cached = 1  one dl4s_cuda_decoder_step per token with key/value caches (fp32): one token of work per step,
+ *               per-token LayerNorm statistics (see above), so the sequence may differ from cached = 0. */
+dl4s_status dl4s_cuda_transformer_greedy_decode(const int32_t *input_ids, int64_t n_in, int32_t start_token, int32_t end_token,
+                                                int64_t max_length, int64_t vocab, int64_t D, int64_t H, int64_t dk, int64_t dv,
+                                                int64_t F, int64_t enc_layers, int64_t dec_layers, const float *d_embedding,
+                                                const float *d_enc_params, const float *d_dec_params, int32_t act,
+                                                int32_t precision, int32_t cached, int32_t *tokens, int64_t *n_tokens);
 
 /* Output head of the Transformer (NN/Models/Transformer/Transformer.swift:105-108):
  *   d_out [M, V] = logSoftmax(d_x [M, D] . d_embedding[V, D]^T + d_bias [V]) over the vocabulary,

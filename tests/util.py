@@ -75,3 +75,25 @@ def unpack_layers(flat, D, H, dk, dv, F, L):
         out.append(layer)
     assert off == flat.size
     return out
+
+
+def dropout_keep_mask(shape, rate, seed, counter):
+    """The device's dropout mask regenerated on the host: the 32-bit hash documented in include/dl4s_cuda.h over the
+    row-major element index, kept where hash < floor((1 - rate) * 2^32). Returns float32 0/1 of `shape`."""
+    n = int(np.prod(shape))
+    i = np.arange(n, dtype=np.uint64)
+    M = np.uint64(0xFFFFFFFF)
+    lo = (i & M).astype(np.uint64)
+    hi = (i >> np.uint64(32)).astype(np.uint64)
+    seed = int(seed)
+    h = (lo * np.uint64(0x9E3779B1) + np.uint64(seed & 0xFFFFFFFF)) & M
+    h ^= h >> np.uint64(16); h = (h * np.uint64(0x85EBCA6B)) & M
+    h ^= h >> np.uint64(13); h = (h * np.uint64(0xC2B2AE35)) & M
+    h ^= h >> np.uint64(16)
+    h = (h + ((hi ^ np.uint64(counter)) & M) * np.uint64(0x27D4EB2F) + np.uint64((seed >> 32) & 0xFFFFFFFF)) & M
+    h ^= h >> np.uint64(15); h = (h * np.uint64(0x2C1B3C6D)) & M
+    h ^= h >> np.uint64(12); h = (h * np.uint64(0x297A2D39)) & M
+    h ^= h >> np.uint64(15)
+    keep = (1.0 - float(np.float32(rate))) * 4294967296.0
+    thr = 0xFFFFFFFF if keep >= 4294967295.0 else max(1, int(keep))
+    return (h < np.uint64(thr)).astype(np.float32).reshape(shape)

@@ -4,9 +4,9 @@ the reference applies them (TransformerDecoderBlock.swift:61-68, Transformer.swi
 import numpy as np
 import pytest
 
-from dl4s_b200 import PREC_F16, PREC_FP32
+from dl4s_b200 import PREC_F16, PREC_F16_SPLIT, PREC_FP32
 from dl4s_b200.layers import Transformer, TransformerDecoder, decoder_layer_weights, encoder_layer_weights
-from util import assert_fp32, assert_tc
+from util import assert_fp32, assert_tc, assert_tc_deep_f16
 
 pytestmark = pytest.mark.gpu
 
@@ -38,7 +38,7 @@ def oracle_mha_rows(O, xq, xkv, Wq, Wk, Wv, Wo, g, s, H, mask):
     return O.layernorm(pre, g, s).reshape(B, Sq, D)          # 2-D input: statistics per row
 
 
-@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16], ids=["fp32", "f16"])
+@pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16, PREC_F16_SPLIT], ids=["fp32", "f16", "f16_split"])
 def test_decoder_forward_against_oracle(dev, oracle, prec):
     rng = np.random.default_rng(60)
     B, St, Ss, D, H, dk, F, L = 3, 128, 160, 128, 2, 64, 256, 2
@@ -49,7 +49,9 @@ def test_decoder_forward_against_oracle(dev, oracle, prec):
     dec = TransformerDecoder(L, H, dk, dk, D, F, layers=layers, precision=prec)
     got = dec(dev.tensor(x), dev.tensor(enc), enc_lens, dec_lens).numpy()
     want = oracle_decoder(oracle, x, enc, layers, H, enc_lens, dec_lens)
-    (assert_fp32 if prec == PREC_FP32 else assert_tc)(got, want, "decoder 2 x [3,128,128] over encoder states [3,160,128]")
+    # six sublayers deep: single-rounded weights are held to their documented figure, split weights to the stated one
+    check = {PREC_FP32: assert_fp32, PREC_F16: assert_tc_deep_f16, PREC_F16_SPLIT: assert_tc}[prec]
+    check(got, want, "decoder 2 x [3,128,128] over encoder states [3,160,128]")
     assert dev.device_status() == 0
 
 

@@ -104,7 +104,7 @@ def test_encoder_and_embedding_with_dropout(dev, oracle, prec):
     L.setDropout(rate, seed)
     L.dropoutCounter(set_to=0)
     x_dev = emb(dev.tensor(c["ids"], np.int32))                       # site 0: the embedded inputs
-    x = (c["x"] * dropout_keep_mask(c["x"].shape, rate, seed, 0)).astype(np.float32)
+    x = (oracle.embed(c["ids"], c["embedding"], -1) * dropout_keep_mask(c["x"].shape, rate, seed, 0)).astype(np.float32)
     assert_fp32(x_dev.numpy(), x, "embedded inputs with dropout")
     got = enc(x_dev, c["lengths"]).numpy()
     assert L.dropoutCounter() == 5

@@ -46,6 +46,17 @@ def assert_tc(got, want, what=""):
     assert_close(got, want, TC_MAX_ABS, TC_REL_L2, what)
 
 
+# Stacks of more than two sublayers on DL4S_PREC_F16 (weights rounded to half once): the relative L2 error stays inside
+# 1e-3 but the largest single deviation grows past 2e-3 (measured 3.1e-3 on the 6-layer encoder at batch 32 x 512,
+# 2.8e-3 on a 2-layer decoder = 6 sublayers). This is that measured figure with a margin, NOT a tolerance of the
+# path: DL4S_PREC_F16_SPLIT is the mode that meets the stated 2e-3 at depth, and the tests hold it to that.
+F16_DEEP_MAX_ABS_DOCUMENTED = 3.5e-3
+
+
+def assert_tc_deep_f16(got, want, what=""):
+    assert_close(got, want, F16_DEEP_MAX_ABS_DOCUMENTED, TC_REL_L2, what)
+
+
 def assert_fp32_rel(got, want, what=""):
     """For EngineType primitives whose results are not O(1) (a product over K = 2048 terms, a sum over 10^5
     elements, exp of 10): fp32 cannot hold 1e-5 absolute there (one ulp of 100 is 8e-6), so the bound is relative to

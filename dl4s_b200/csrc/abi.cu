@@ -278,6 +278,7 @@ dl4s_status dl4s_cuda_device_status(int32_t *status_word)
     DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
     if (status_word) *status_word = w;
     if (w & kStatusTimeoutMask) return fail(DL4S_ERR_TIMEOUT, "a bounded device-side wait gave up (status word 0x%x)", w);
+    if (w & 0xF0000) return fail(DL4S_ERR_TIMEOUT, "a bounded device-side wait gave up (status word 0x%x)", w);
     if (w & kStatusCacheFull) return fail(DL4S_ERR_INVALID_ARG, "a decode step found its key/value cache full (status word 0x%x)", w);
     if (w & kStatusHalfRange)
         return fail(DL4S_ERR_INVALID_ARG, "a tensor-core operand left the IEEE half range (|x| >= 65504 or not finite): the results of "

@@ -11,6 +11,7 @@
 // in a fixed order: the result does not depend on scheduling. This is the fp32 reference path for
 // training on the device; it materialises the score matrix like the CPU engine does.
 #include "common.cuh"
+#include "tc.cuh"
 
 namespace dl4s {
 
@@ -227,7 +228,7 @@ using namespace dl4s;
 extern "C" dl4s_status dl4s_cuda_sdpa_backward(const float *d_q, const float *d_k, const float *d_v, const float *d_dout, int64_t B,
                                                int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv, float temperature,
                                                const int32_t *d_key_lengths, int32_t causal, const float *d_mask,
-                                               const int64_t *mask_shape, float *d_dq, float *d_dk, float *d_dv)
+                                               const int64_t *mask_shape, float *d_dq, float *d_dk, float *d_dv, int32_t precision)
 {
     DL4S_STATE(st);
     DL4S_REQUIRE(d_q && d_k && d_v && d_dout && d_dq && d_dk && d_dv, "NULL buffer");
@@ -247,6 +248,13 @@ extern "C" dl4s_status dl4s_cuda_sdpa_backward(const float *d_q, const float *d_
             mask.ms[i] = mask_shape[i];
         }
     }
+    DL4S_REQUIRE(precision == DL4S_PREC_FP32 || precision == DL4S_PREC_F16 || precision == DL4S_PREC_F16_SPLIT,
+                 "unknown precision %d", precision);
     ScopedTimer timer(st);
+    // Tensor-core path: structural masks, head sizes 64 / 128 (no weights are involved, so the two tensor-core
+    // precisions are the same here); everything else runs on the fp32 kernels.
+    if (precision != DL4S_PREC_FP32 && !d_mask && dk == dv && attn_bwd_tc_supported(Sq, Sk, dk, dv) && B * H <= 65535 &&
+        (((uintptr_t)d_q | (uintptr_t)d_k | (uintptr_t)d_v | (uintptr_t)d_dout | (uintptr_t)d_dq | (uintptr_t)d_dk | (uintptr_t)d_dv) & 15) == 0)
+        return launch_attn_bwd_tc(st, d_q, d_k, d_v, d_dout, B, H, Sq, Sk, dk, 1.0f / temperature, mask, d_dq, d_dk, d_dv);
     return launch_attn_bwd_ref(st, d_q, d_k, d_v, d_dout, B, H, Sq, Sk, dk, dv, 1.0f / temperature, mask, d_dq, d_dk, d_dv);
 }

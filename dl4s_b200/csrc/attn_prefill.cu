@@ -72,6 +72,19 @@ __global__ void __launch_bounds__(256) k_pack_heads_f16(const float *__restrict_
     }
 }
 
+dl4s_status pack_heads_f16(DeviceState *st, const float *src, Strides4 ss, void *dst, int64_t BH, int64_t H, int64_t S, int D,
+                           float scale)
+{
+    int64_t total_vec = BH * S * (D / 8);
+    if (total_vec == 0) return DL4S_OK;
+    int64_t blocks = ceil_div(total_vec, 256 * 4);
+    int64_t cap = (int64_t)st->sm_count * 8;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    k_pack_heads_f16<<<(unsigned)blocks, 256, 0, st->stream>>>(src, ss, (__half *)dst, H, S, D, scale, total_vec);
+    return after_launch(st, "k_pack_heads_f16");
+}
+
 struct AttnTcParams {
     void *o;                 // float (o_half == 0) or half (o_half == 1), strides in elements
     int o_half;
@@ -83,6 +96,7 @@ struct AttnTcParams {
     int nqb;                 // blocks of NT x 128 query rows
     int BH;                  // batch * heads
     int32_t *status;
+    float *lse;              // optional [B*H, Sq]: log2 of each row's softmax denominator, in the kernel's base-2 score units
 };
 
 __device__ __forceinline__ float fast_exp2(float x)
@@ -441,6 +455,8 @@ __global__ void __launch_bounds__(at_threads(NT), NT == 2 ? 1 : 2) k_attn_prefil
         if (ok && n_t > 0) {
             tc_fence_after();
             const float inv_l = 1.0f / l_sum;
+            // what the backward pass needs to recompute the probabilities: p = 2^(s - lse)
+            if (p.lse && row < p.Sq) p.lse[(int64_t)bh * p.Sq + row] = m_used + log2f(l_sum);
             const int64_t ooff = (int64_t)b * p.os.b + (int64_t)h * p.os.h + (int64_t)row * p.os.s;
             float *orow = reinterpret_cast<float *>(p.o) + ooff;
             __half *hrow = reinterpret_cast<__half *>(p.o) + ooff;
@@ -529,13 +545,7 @@ dl4s_status launch_attn_prefill_tc(DeviceState *st, const float *q, Strides4 qs,
     __half *kh = (__half *)((char *)qh + align_up((size_t)(BH * Sq * D) * 2, 1024));
     __half *vh = (__half *)((char *)kh + align_up((size_t)(BH * Sk * D) * 2, 1024));
     auto pack = [&](const float *src, Strides4 ss, __half *dst, int64_t S, float scale) -> dl4s_status {
-        int64_t total_vec = BH * S * (D / 8);
-        int64_t blocks = ceil_div(total_vec, 256 * 4);
-        int64_t cap = (int64_t)st->sm_count * 8;
-        if (blocks > cap) blocks = cap;
-        if (blocks < 1) blocks = 1;
-        k_pack_heads_f16<<<(unsigned)blocks, 256, 0, st->stream>>>(src, ss, dst, H, S, D, scale, total_vec);
-        return after_launch(st, "k_pack_heads_f16");
+        return pack_heads_f16(st, src, ss, dst, BH, H, S, D, scale);
     };
     DL4S_TRY(pack(q, qs, qh, Sq, inv_temperature * kLog2e));
     DL4S_TRY(pack(k, ks, kh, Sk, 1.0f));
@@ -546,7 +556,8 @@ dl4s_status launch_attn_prefill_tc(DeviceState *st, const float *q, Strides4 qs,
 float attn_prefill_tc_q_scale(float inv_temperature) { return inv_temperature * kLog2e; }
 
 dl4s_status launch_attn_prefill_tc_h(DeviceState *st, const void *qh, const void *kh, const void *vh, void *o, Strides4 os,
-                                     int o_half, int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t D, const MaskSpec &mask)
+                                     int o_half, int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t D, const MaskSpec &mask,
+                                     float *lse)
 {
     DL4S_REQUIRE(attn_prefill_tc_supported(Sq, Sk, D, D), "shape not supported by the tensor-core attention");
     DL4S_REQUIRE(!mask.d_mask, "dense masks are not supported by the tensor-core attention");
@@ -566,6 +577,7 @@ dl4s_status launch_attn_prefill_tc_h(DeviceState *st, const void *qh, const void
     p.lens = mask.d_key_lengths;
     p.causal = mask.causal;
     p.status = st->status_word;
+    p.lse = lse;
     if (D == 128) {
         p.nqb = (int)ceil_div(Sq, 2 * AT_TILE);
         return run_attn_tc<128, 2>(st, tq, tk, tv, p, BH);

@@ -97,6 +97,8 @@ struct CommState {
     int last_chunks = 0;
     void *gather = nullptr;
     size_t gather_bytes = 0;
+    void *xh = nullptr;           // half copy of the replicated input of the current call (tensor-core paths)
+    size_t xh_bytes = 0;
 };
 static CommState g_comm[kMaxDevices];
 
@@ -133,7 +135,7 @@ static int make_plan(int64_t B, int world, int rank, int chunks, ChunkPlan *plan
 void comm_release_device(int ordinal)
 {
     CommState &c = g_comm[ordinal];
-    if (!c.live && !c.gather) return;
+    if (!c.live && !c.gather && !c.xh) return;
     if (c.stream) cudaStreamSynchronize(c.stream);
     if (c.comm && g_nccl.comm_destroy) g_nccl.comm_destroy(c.comm);
     for (int i = 0; i < kMaxChunks; ++i) {
@@ -142,6 +144,7 @@ void comm_release_device(int ordinal)
     }
     if (c.stream) cudaStreamDestroy(c.stream);
     if (c.gather) cudaFree(c.gather);
+    if (c.xh) cudaFree(c.xh);
     c = CommState();
 }
 
@@ -171,9 +174,10 @@ dl4s_status dl4s_cuda_comm_init(int32_t rank, int32_t world, const uint8_t *id)
     DL4S_REQUIRE(!st->capturing, "join the communicator before dl4s_cuda_graph_begin");
     CommState &c = g_comm[st->ordinal];
     DL4S_REQUIRE(!c.live, "device %d already belongs to a communicator: call dl4s_cuda_comm_destroy first", st->ordinal);
-    if (c.gather) {   // left by calls made as a world of one before joining
+    if (c.gather || c.xh) {   // left by calls made as a world of one before joining
         DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
-        DL4S_CUDA_TRY(cudaFree(c.gather));
+        if (c.gather) DL4S_CUDA_TRY(cudaFree(c.gather));
+        if (c.xh) DL4S_CUDA_TRY(cudaFree(c.xh));
     }
     c = CommState();
     c.rank = rank;
@@ -200,7 +204,7 @@ dl4s_status dl4s_cuda_comm_destroy(void)
 {
     DL4S_STATE(st);
     CommState &c = g_comm[st->ordinal];
-    if (!c.live && !c.gather) return DL4S_OK;
+    if (!c.live && !c.gather && !c.xh) return DL4S_OK;
     cudaStreamSynchronize(st->stream);
     if (c.stream) cudaStreamSynchronize(c.stream);
     dl4s_status result = DL4S_OK;
@@ -211,6 +215,7 @@ dl4s_status dl4s_cuda_comm_destroy(void)
     }
     if (c.stream) cudaStreamDestroy(c.stream);
     if (c.gather) cudaFree(c.gather);
+    if (c.xh) cudaFree(c.xh);
     c = CommState();
     return result;
 }
@@ -313,14 +318,32 @@ dl4s_status dl4s_cuda_mha_forward_sharded(const float *d_x, int64_t B, int64_t S
         c.gather_bytes = (size_t)nchunks * chunk_bytes;
     }
     ScopedGroup group(st, "MultiHeadAttention");
+    // Tensor-core paths: the replicated input is rounded to half ONCE per call, in one pass at full HBM speed before
+    // any gather is in flight, instead of chunk by chunk under the gathers' traffic (every rank needs all of it
+    // for its projections, so this pass does not shrink with the number of ranks).
+    const void *xh = nullptr;
+    if (half && nchunks > 1) {
+        const size_t need = (size_t)(B * S * D) * 2;
+        if (need > c.xh_bytes) {
+            DL4S_CUDA_TRY(cudaStreamSynchronize(st->stream));
+            if (c.xh) DL4S_CUDA_TRY(cudaFree(c.xh));
+            c.xh = nullptr;
+            c.xh_bytes = 0;
+            DL4S_CUDA_TRY(cudaMalloc(&c.xh, need));
+            c.xh_bytes = need;
+        }
+        DL4S_TRY(launch_f32_to_f16(st, d_x, c.xh, B * S * D));
+        xh = c.xh;
+    }
 
     auto gathered = [&](int i) { return static_cast<char *>(c.gather) + (size_t)i * chunk_bytes; };
     auto heads = [&](int i) -> dl4s_status {
         const int64_t c0 = plan[i].c0, Bc = plan[i].c1 - plan[i].c0;
         const float *xp = d_x + c0 * S * D;
         void *slot = gathered(i) + (size_t)(rank * Bc * S * C) * esz;
-        return dl4s_cuda_mha_heads_forward(xp, xp, xp, Bc, S, S, D, Hl, dk, dv, d_wq_local, d_wk_local, d_wv_local,
-                                           d_key_lengths ? d_key_lengths + c0 : nullptr, causal, slot, precision, half);
+        return mha_heads_forward_impl(xp, xp, xp, Bc, S, S, D, Hl, dk, dv, d_wq_local, d_wk_local, d_wv_local,
+                                      d_key_lengths ? d_key_lengths + c0 : nullptr, causal, slot, precision, half,
+                                      xh ? static_cast<const char *>(xh) + (size_t)(c0 * S * D) * 2 : nullptr);
     };
     // ONE collective per chunk: in-place all-gather of the head outputs on the second stream.
     auto gather = [&](int i) -> dl4s_status {

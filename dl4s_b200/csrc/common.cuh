@@ -284,6 +284,14 @@ dl4s_status launch_attn_decode(DeviceState *st, const float *q, const float *k, 
                                const int32_t *d_key_lengths, float *out, float *scratch, int64_t chunk,
                                int64_t nsplit);
 
+// fused.cu: dl4s_cuda_mha_heads_forward with an optional half copy of the input held by the caller.
+dl4s_status mha_heads_forward_impl(const float *d_xq, const float *d_xk, const float *d_xv, int64_t B, int64_t Sq, int64_t Sk,
+                                   int64_t D, int64_t Hl, int64_t dk, int64_t dv, const float *d_wq, const float *d_wk,
+                                   const float *d_wv, const int32_t *d_key_lengths, int32_t causal, void *d_heads_out,
+                                   int32_t precision, int32_t half_output, const void *d_x_half);
+// gemm_tc.cu: fp32 -> half, 16-byte aligned buffers.
+dl4s_status launch_f32_to_f16(DeviceState *st, const float *x, void *y, int64_t n);
+
 // comm.cu: frees a device's communicator, second stream and gather buffers.
 void comm_release_device(int ordinal);
 

@@ -323,12 +323,12 @@ dl4s_status mha_self_tc(DeviceState *st, const float *x, int64_t B, int64_t S, i
 // one fused q/k/v product into head-major halves, attention, result [B,S,H*dv] as fp32 or half.
 dl4s_status mha_heads_self_tc(DeviceState *st, const float *x, int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk,
                               int64_t dv, const float *wq, const float *wk, const float *wv, const MaskSpec &mask, void *out,
-                              int out_half, int split)
+                              int out_half, int split, const void *x_half)
 {
     const int Nq = (int)(H * dk), Nv = (int)(H * dv);
     auto layout = [&](Bump &bp, void **w, void **xh, void **qh, void **kh, void **vh) {
         *w = bp.take((size_t)(D * (2 * Nq + Nv)) * (split ? 4 : 2));
-        *xh = bp.take((size_t)(B * S * D) * 2);
+        *xh = x_half ? nullptr : bp.take((size_t)(B * S * D) * 2);   // the caller may hold the half copy already
         *qh = bp.take((size_t)(B * H * S * dk) * 2);
         *kh = bp.take((size_t)(B * H * S * dk) * 2);
         *vh = bp.take((size_t)(B * H * S * dv) * 2);
@@ -342,7 +342,8 @@ dl4s_status mha_heads_self_tc(DeviceState *st, const float *x, int64_t B, int64_
     Bump bp(base);
     layout(bp, &w, &xh, &qh, &kh, &vh);
     DL4S_TRY(concat_cols_f16(st, wq, Nq, wk, Nq, wv, Nv, D, w, split));
-    DL4S_TRY(launch_f32_to_f16(st, x, xh, B * S * D));
+    if (x_half) xh = const_cast<void *>(x_half);
+    else DL4S_TRY(launch_f32_to_f16(st, x, xh, B * S * D));
     GemmTcOut o;
     o.mode = OUT_HEADS_F16;
     o.H = (int)H; o.S = (int)S; o.nparts = 3;

@@ -378,10 +378,15 @@ dl4s_status dl4s_cuda_mha_forward(const float *d_xq, const float *d_xk, const fl
                (char *)base + main_bytes, extra);
 }
 
-dl4s_status dl4s_cuda_mha_heads_forward(const float *d_xq, const float *d_xk, const float *d_xv, int64_t B, int64_t Sq,
-                                        int64_t Sk, int64_t D, int64_t Hl, int64_t dk, int64_t dv, const float *d_wq,
-                                        const float *d_wk, const float *d_wv, const int32_t *d_key_lengths, int32_t causal,
-                                        void *d_heads_out, int32_t precision, int32_t half_output)
+}  // extern "C"
+
+namespace dl4s {
+// dl4s_cuda_mha_heads_forward with an optional half copy of the (self-attention) input that the caller already holds:
+// the layer that spans GPUs rounds its whole replicated input once per call instead of once per batch chunk.
+dl4s_status mha_heads_forward_impl(const float *d_xq, const float *d_xk, const float *d_xv, int64_t B, int64_t Sq, int64_t Sk,
+                                   int64_t D, int64_t Hl, int64_t dk, int64_t dv, const float *d_wq, const float *d_wk,
+                                   const float *d_wv, const int32_t *d_key_lengths, int32_t causal, void *d_heads_out,
+                                   int32_t precision, int32_t half_output, const void *d_x_half)
 {
     DL4S_STATE(st);
     DL4S_REQUIRE(d_xq && d_xk && d_xv && d_wq && d_wk && d_wv && d_heads_out, "NULL buffer");
@@ -393,7 +398,7 @@ dl4s_status dl4s_cuda_mha_heads_forward(const float *d_xq, const float *d_xk, co
     if (fused_tc) {
         ScopedTimer timer(st);
         return mha_heads_self_tc(st, d_xq, B, Sq, D, Hl, dk, dv, d_wq, d_wk, d_wv, mask, d_heads_out, half_output != 0,
-                                 prec_split(precision));
+                                 prec_split(precision), d_x_half);
     }
     if (half_output)
         return fail(DL4S_ERR_UNSUPPORTED, "half output needs the fused tensor-core path (see dl4s_cuda_mha_heads_half_supported)");
@@ -405,6 +410,19 @@ dl4s_status dl4s_cuda_mha_heads_forward(const float *d_xq, const float *d_xk, co
     ScopedTimer timer(st);
     return mha_heads(st, d_xq, d_xk, d_xv, s, d_wq, d_wk, d_wv, mask, (float *)d_heads_out, precision, (float *)base,
                      (char *)base + main_bytes, extra);
+}
+
+}  // namespace dl4s
+
+extern "C" {
+
+dl4s_status dl4s_cuda_mha_heads_forward(const float *d_xq, const float *d_xk, const float *d_xv, int64_t B, int64_t Sq,
+                                        int64_t Sk, int64_t D, int64_t Hl, int64_t dk, int64_t dv, const float *d_wq,
+                                        const float *d_wk, const float *d_wv, const int32_t *d_key_lengths, int32_t causal,
+                                        void *d_heads_out, int32_t precision, int32_t half_output)
+{
+    return mha_heads_forward_impl(d_xq, d_xk, d_xv, B, Sq, Sk, D, Hl, dk, dv, d_wq, d_wk, d_wv, d_key_lengths, causal, d_heads_out,
+                                  precision, half_output, nullptr);
 }
 
 dl4s_status dl4s_cuda_mha_heads_half_supported(int64_t B, int64_t S, int64_t D, int64_t Hl, int64_t dk, int64_t dv, int64_t HDv,

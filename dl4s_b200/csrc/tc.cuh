@@ -61,8 +61,22 @@ dl4s_status launch_attn_prefill_tc(DeviceState *st, const float *q, Strides4 qs,
 // (pre-multiplied by attn_prefill_tc_q_scale), kh, vh [B*H,Sk,D]. The output goes to
 // `o` with (batch, head, row) strides in elements, as fp32 or (o_half != 0) as half.
 float attn_prefill_tc_q_scale(float inv_temperature);
+// `lse` (optional, [B*H, Sq]): log2 of every row's softmax denominator in base-2 score units (scores = qh . kh), which
+// is what the backward kernel needs to recompute the probabilities.
 dl4s_status launch_attn_prefill_tc_h(DeviceState *st, const void *qh, const void *kh, const void *vh, void *o, Strides4 os,
-                                     int o_half, int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t D, const MaskSpec &mask);
+                                     int o_half, int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t D, const MaskSpec &mask,
+                                     float *lse = nullptr);
+
+// Strided fp32 [B,H,S,D] -> contiguous half [B*H,S,D], multiplied by `scale`.
+dl4s_status pack_heads_f16(DeviceState *st, const float *src, Strides4 ss, void *dst, int64_t BH, int64_t H, int64_t S, int D,
+                           float scale);
+
+// attn_bwd_tc.cu — flash-style backward of the same attention on the tensor cores: dq, dk, dv [B,H,S,D] fp32
+// (contiguous) from q, k, v, dout (fp32, contiguous) with structural masks; the probabilities are recomputed.
+bool attn_bwd_tc_supported(int64_t Sq, int64_t Sk, int64_t dk, int64_t dv);
+dl4s_status launch_attn_bwd_tc(DeviceState *st, const float *q, const float *k, const float *v, const float *dout, int64_t B,
+                               int64_t H, int64_t Sq, int64_t Sk, int64_t D, float inv_temperature, const MaskSpec &mask, float *dq,
+                               float *dk, float *dv);
 
 // encoder_tc.cu — the fused tensor-core pipelines (intermediates in half, no conversion passes).
 // They reserve their own scratch from the device arena.
@@ -73,7 +87,7 @@ dl4s_status mha_self_tc(DeviceState *st, const float *x, int64_t B, int64_t S, i
                         const MaskSpec &mask, float *out, int split);
 dl4s_status mha_heads_self_tc(DeviceState *st, const float *x, int64_t B, int64_t S, int64_t D, int64_t H, int64_t dk,
                               int64_t dv, const float *wq, const float *wk, const float *wv, const MaskSpec &mask, void *out,
-                              int out_half, int split);
+                              int out_half, int split, const void *x_half = nullptr);
 dl4s_status mha_output_tc(DeviceState *st, const void *heads, int heads_half, const float *residual, int64_t B, int64_t S,
                           int64_t D, int64_t HDv, const float *wo, const float *g, const float *sh, float *out,
                           int64_t groups, int64_t group_stride, int split);

@@ -337,14 +337,19 @@ dl4s_status dl4s_cuda_mha_forward(const float *d_xq, const float *d_xk, const fl
  * (Unary.swift:190-194) and the division by the temperature, in one call:
  *   d_dout [B,H,Sq,dv] -> d_dq [B,H,Sq,dk], d_dk [B,H,Sk,dk], d_dv [B,H,Sk,dv]
  * for contiguous q, k, v and the same mask arguments as dl4s_cuda_sdpa_forward. The probabilities are
- * recomputed (the forward call keeps nothing). fp32 FFMA kernels (agree with the CPU engine's gradients to
- * 1e-5); scratch of 2*B*H*Sq*Sk floats comes from the device arena; head sizes up to 256. A tensor-core
- * backward does not exist yet. */
+ * recomputed (the forward call keeps nothing).
+ *  DL4S_PREC_FP32: fp32 FFMA kernels (agree with the CPU engine's gradients to 1e-5); scratch of 2*B*H*Sq*Sk
+ *                  floats from the device arena; head sizes up to 256; dense masks.
+ *  DL4S_PREC_F16 / _SPLIT: flash-style tensor-core kernel (dk == dv in {64, 128}, structural masks, 16-byte
+ *                  aligned buffers; otherwise the fp32 kernels run): per key tile S = Q K^T and dP = dout V^T are
+ *                  recomputed, dV += P^T dout, dK += dS^T Q, dQ += dS K with tcgen05 MMAs, nothing of size Sq x Sk
+ *                  is stored. dq rows are summed over key tiles with atomic adds (last-bit differences between
+ *                  runs); dk and dv are summed in a fixed order. */
 dl4s_status dl4s_cuda_sdpa_backward(const float *d_q, const float *d_k, const float *d_v, const float *d_dout,
                                     int64_t B, int64_t H, int64_t Sq, int64_t Sk, int64_t dk, int64_t dv,
                                     float temperature, const int32_t *d_key_lengths, int32_t causal,
                                     const float *d_mask, const int64_t *mask_shape,
-                                    float *d_dq, float *d_dk, float *d_dv);
+                                    float *d_dq, float *d_dk, float *d_dv, int32_t precision);
 
 /* The two halves of MultiHeadAttention.callAsFunction around the point where a
  * layer that spans GPUs exchanges data (MultiHeadAttention.swift:109-119 and

@@ -869,6 +869,50 @@ def run_gemm(args, gpu, peaks):
                          "frac": ach / peaks["tflops_burst"] if ach else None, "traffic": None, "ms_kernel": ms_kernel}}
 
 
+def run_backward(args, gpu, peaks):
+    """Attention backward (dq, dk, dv from an upstream gradient, probabilities recomputed) on the tensor cores, at the
+    attention shape of the encoder configuration (batch 32, 8 heads, seq 512, d 64, padding mask) or --shape B,H,S,d
+    with a causal mask. The call includes packing the operands to half, one forward pass (outputs and softmax
+    denominators) and the delta pass; the kernel figure is the backward kernel alone. FLOPs: five products per
+    (query, key) pair that the mask lets through = 10 d per pair."""
+    from dl4s_b200 import PREC_F16
+    from dl4s_b200.layers import scaledDotProductAttentionBackward
+    cuda = gpu.cuda
+    shape = [int(v) for v in args.shape.split(",")] if args.shape else None
+    B, H, S, d = shape or (32, 8, 512, 64)
+    causal = shape is not None
+    rng = np.random.default_rng(1)
+    q, k, v, g = (cuda.tensor(rng.standard_normal((B, H, S, d), dtype=np.float32)) for _ in range(4))
+    if causal:
+        mask, pairs = cuda.StructuredMask(None, causal=True), B * H * (S * (S + 1) // 2)
+    else:
+        lens = np.random.default_rng(3).integers(S // 2, S + 1, size=B).astype(np.int32)
+        lens[0] = S
+        mask, pairs = cuda.makeEncoderMasks(lens), H * S * int(lens.sum())
+    temperature = float(np.sqrt(np.float32(d)))
+
+    def call():
+        scaledDotProductAttentionBackward(q, k, v, g, mask, temperature, PREC_F16)
+
+    flops = 10 * d * pairs
+    ms_kernel, _ = kernel_time(gpu, call, "k_attn_bwd_tc", max(args.steps, 3))
+    total_ms = gpu.timed_steps(call, args.steps, args.warmup) / args.steps
+    cuda.profile_begin()
+    call()
+    prof = cuda.profile_end()
+    ach = flops / (ms_kernel * 1e-3) / 1e12 if ms_kernel else None
+    return {"metric": "attention_backward_tflops", "value": flops / (total_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": gpu.world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32 in/out; f16 tensor-core operands, f32 accumulate", "data": "synthetic",
+            "config": {"workload": f"attention backward B{B} H{H} S{S} d{d}, {'causal' if causal else 'padding mask, lengths U[S/2,S]'}",
+                       "l2": "256 MiB flush write between timed steps", "flops": "10 d per unmasked (query, key) pair"},
+            "roofline": {"bound": "tensor", "kernel": "k_attn_bwd_tc", "achieved": ach, "peak": peaks["tflops_burst"], "unit": "TFLOP/s",
+                         "frac": ach / peaks["tflops_burst"] if ach else None, "traffic": None, "ms_kernel": ms_kernel,
+                         "peak_source": peaks["source"] + " bf16 dense burst"},
+            "gpu_launches": gpu.last_timed_launches,
+            "kernel_profile_ms_per_step": {k2: round(v2["total_ms"], 4) for k2, v2 in prof.items()}}
+
+
 def cpu_attention_slice(workload, B, H, S, d):
     """DL4S's CPU engine cannot hold these problems (it materialises the [B,H,Sq,Sk] scores several times), so ONE
     slice is timed on one host core with the generic engine and the whole problem is a linear extrapolation:
@@ -927,7 +971,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="encoder", choices=["encoder", "prefill", "decode", "decoder_mha", "gemm", "mha", "decode_step", "head"])
+    ap.add_argument("--workload", default="encoder", choices=["encoder", "prefill", "decode", "decoder_mha", "gemm", "mha", "decode_step", "head", "backward"])
     ap.add_argument("--precision", default="f16", choices=["f16", "f16_split", "fp32"],
                     help="f16: half operands rounded once; f16_split: weights as two halves (meets max-abs 2e-3 on the 6-layer "
                          "encoder); fp32: FFMA check kernels")
@@ -958,6 +1002,8 @@ def main():
         line = run_decode_step(args, gpu, peaks)
     elif args.workload == "head":
         line = run_output_head(args, gpu, peaks)
+    elif args.workload == "backward":
+        line = run_backward(args, gpu, peaks)
     else:
         line = run_attention_only(args, gpu, peaks)
     status = gpu.cuda.device_status()

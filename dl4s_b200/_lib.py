@@ -99,6 +99,7 @@ _SIGNATURES = {
                                 c_i64p, c_vp, c_vp, c_vp, c_i32],
     "dl4s_cuda_sdpa_decode": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_f32, c_vp, c_vp],
     "dl4s_cuda_sdpa_decode_noalloc": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_f32, c_vp, c_vp],
+    "dl4s_cuda_layernorm_backward": [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp, c_vp],
     "dl4s_cuda_layernorm": [c_vp, c_vp, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp],
     "dl4s_cuda_mha_forward": [c_vp, c_vp, c_vp, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_i64, c_vp, c_vp, c_vp,
                               c_vp, c_vp, c_vp, c_vp, c_i32, c_vp, c_i64p, c_vp, c_i32],

@@ -248,6 +248,14 @@ dl4s_status dl4s_cuda_gemm(const float *d_a, const float *d_b, float *d_c, int64
         DL4S_TRY(arena_reserve(st, need, &scratch));
         return launch_gemm_tc(st, d_a, d_b, d_c, M, N, K, EPI_NONE, nullptr, nullptr, scratch, need, prec_split(precision));
     }
+    if (prec_tc(precision) && alpha == 1.0f && beta == 0.0f && gemm_tc_trans_supported(M, N, K, trans_a, trans_b) &&
+        (((uintptr_t)d_a | (uintptr_t)d_b | (uintptr_t)d_c) & 15) == 0) {
+        // the products of a matmul's backward (dA = dC B^T, dB = A^T dC, Matrix.swift:139-173) on the tensor cores
+        size_t need = gemm_tc_scratch_bytes(M, N, K, 0);
+        void *scratch = nullptr;
+        DL4S_TRY(arena_reserve(st, need, &scratch));
+        return launch_gemm_tc_trans(st, d_a, d_b, d_c, M, N, K, trans_a, trans_b, scratch, need);
+    }
     return launch_gemm_f32(st, d_a, d_b, d_c, M, N, K, alpha, beta, trans_a, trans_b, EPI_NONE, nullptr, nullptr);
 }
 

@@ -193,10 +193,16 @@ __host__ __device__ constexpr int gemm_stages(int BN, int PAIR) { return (PAIR |
 // (cta_group::2) issued by the leader (cluster rank 0). Each CTA loads its 128 rows of A and
 // its half of B's columns — per CTA 32 KB per k-block for a 128 x 256 result instead of 48 KB,
 // which is what the L2 -> SM path has to deliver — and drains its own 128 accumulator rows.
-template <int BN, int EPI, int OUT, int PAIR>
+//
+// TA / TB = 1 (single-CTA tiles only): the operand is stored transposed, as the backward of a product needs it
+// (Matrix.swift:139-173: dA = dC B^T, dB = A^T dC). A stored [K, M] arrives as 64 x 64 boxes with m contiguous
+// (an MN-major operand, like B in the plain form); B stored [N, K] arrives as one box of BN rows of 64 k (a K-major
+// operand, like A in the plain form). Only the tensor maps, the tile loads and the descriptors differ.
+template <int BN, int EPI, int OUT, int PAIR, int TA = 0, int TB = 0>
 __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __grid_constant__ CUtensorMap tmap_a,
                                                           const __grid_constant__ CUtensorMap tmap_b, GemmTcParams p)
 {
+    static_assert(!(TA || TB) || !PAIR, "transposed operands are served by single-CTA tiles");
     constexpr int CTAS = PAIR ? 2 : 1;
     constexpr int G_EPI_PARTS = epi_parts(EPI, PAIR);
     constexpr int G_EPI_WARPS = 4 * G_EPI_PARTS;
@@ -206,7 +212,8 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
     constexpr uint32_t B_BYTES = B_BLOCK * (BN_CTA / 64);
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
     constexpr uint32_t TMEM_COLS = 2 * BN;                // two accumulators
-    constexpr uint32_t IDESC = idesc_f16(GM * CTAS, BN, 0, 1);   // A K-major, B MN-major
+    constexpr uint32_t A_BLOCK = GK * 64 * 2;             // TA: 64 k-rows x 64 m
+    constexpr uint32_t IDESC = idesc_f16(GM * CTAS, BN, TA, TB ? 0 : 1);   // plain form: A K-major, B MN-major
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -312,10 +319,20 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                             tma_load_2d_pair(sa + A_BYTES + nb * B_BLOCK, &tmap_b, &full_bar[stage], col0 + nb * 64, kb * GK);
                     } else {
                         mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
-                        tma_load_3d(sa, &tmap_a, &full_bar[stage], kx, row0, kz);
+                        if (TA) {
 #pragma unroll
-                        for (int nb = 0; nb < BN_CTA / 64; ++nb)
-                            tma_load_2d(sa + A_BYTES + nb * B_BLOCK, &tmap_b, &full_bar[stage], col0 + nb * 64, kb * GK);
+                            for (int mb = 0; mb < GM / 64; ++mb)
+                                tma_load_2d(sa + mb * A_BLOCK, &tmap_a, &full_bar[stage], row0 + mb * 64, kb * GK);
+                        } else {
+                            tma_load_3d(sa, &tmap_a, &full_bar[stage], kx, row0, kz);
+                        }
+                        if (TB) {
+                            tma_load_2d(sa + A_BYTES, &tmap_b, &full_bar[stage], kb * GK, col0);
+                        } else {
+#pragma unroll
+                            for (int nb = 0; nb < BN_CTA / 64; ++nb)
+                                tma_load_2d(sa + A_BYTES + nb * B_BLOCK, &tmap_b, &full_bar[stage], col0 + nb * 64, kb * GK);
+                        }
                     }
                     if (++stage == G_STAGES) { stage = 0; phase ^= 1; }
                     kx += GK;
@@ -343,8 +360,8 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                     const uint32_t sb = sa + A_BYTES;
 #pragma unroll
                     for (int k16 = 0; k16 < GK / 16; ++k16) {
-                        uint64_t adesc = smem_desc_sw128(sa + k16 * 32, 16, 1024);
-                        uint64_t bdesc = smem_desc_mn_sw128(sb + k16 * 2048, B_BLOCK, 1024);
+                        uint64_t adesc = TA ? smem_desc_mn_sw128(sa + k16 * 2048, A_BLOCK, 1024) : smem_desc_sw128(sa + k16 * 32, 16, 1024);
+                        uint64_t bdesc = TB ? smem_desc_sw128(sb + k16 * 32, 16, 1024) : smem_desc_mn_sw128(sb + k16 * 2048, B_BLOCK, 1024);
                         if (PAIR) umma_ss_pair(d_tmem, adesc, bdesc, IDESC, (kb | k16) != 0);
                         else umma_ss(d_tmem, adesc, bdesc, IDESC, (kb | k16) != 0);
                     }
@@ -681,7 +698,7 @@ static int64_t gemm_tc_pair_min_k()
     return v;
 }
 
-template <int BN, int EPI, int OUT, int PAIR>
+template <int BN, int EPI, int OUT, int PAIR, int TA = 0, int TB = 0>
 static dl4s_status run_gemm_tc_inst2(DeviceState *st, const CUtensorMap &ta, const CUtensorMap &tb, GemmTcParams p, const char *name)
 {
     constexpr int CTAS = PAIR ? 2 : 1;
@@ -689,7 +706,7 @@ static dl4s_status run_gemm_tc_inst2(DeviceState *st, const CUtensorMap &ta, con
     constexpr size_t smem = (size_t)gemm_stages(BN, PAIR) * (GM * GK * 2 + GK * (BN / CTAS) * 2) + 1024;
     static bool attr_set[kMaxDevices] = {false};
     if (!attr_set[st->ordinal]) {
-        DL4S_CUDA_TRY(cudaFuncSetAttribute(k_gemm_tc<BN, EPI, OUT, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        DL4S_CUDA_TRY(cudaFuncSetAttribute(k_gemm_tc<BN, EPI, OUT, PAIR, TA, TB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         attr_set[st->ordinal] = true;
     }
     p.tiles_m = (int)ceil_div(p.M, GM * CTAS);
@@ -704,7 +721,8 @@ static dl4s_status run_gemm_tc_inst2(DeviceState *st, const CUtensorMap &ta, con
         p.test_skip_kb = p.K / GK > 1 ? 1 : 0;
         p.wait_polls = 1u << 16;
     }
-    DL4S_CUDA_TRY(launch_pdl(st, k_gemm_tc<BN, EPI, OUT, PAIR>, dim3((unsigned)grid), dim3(gemm_threads(EPI, PAIR)), smem, CTAS, ta, tb, p));
+    DL4S_CUDA_TRY(launch_pdl(st, k_gemm_tc<BN, EPI, OUT, PAIR, TA, TB>, dim3((unsigned)grid), dim3(gemm_threads(EPI, PAIR)), smem, CTAS, ta, tb,
+                             p));
     return after_launch(st, name);
 }
 
@@ -823,6 +841,57 @@ dl4s_status launch_gemm_tc(DeviceState *st, const float *a, const float *b, floa
     out.mode = OUT_F32;
     out.c = c;
     return launch_gemm_tc_h(st, ah, bh, M, N, K, epilogue, bias, residual, out, 1, 0, split, drop);
+}
+
+// C = op(A) op(B) with at least one operand stored transposed (the shapes the backward of a product takes,
+// Matrix.swift:139-173): A stored [K, M] when trans_a, B stored [N, K] when trans_b; fp32 in and out, operands rounded
+// to half in their stored layout. Single-CTA tiles; needs what gemm_tc_supported asks plus M % 8 == 0 when trans_a
+// (the TMA row stride of the stored matrix).
+bool gemm_tc_trans_supported(int64_t M, int64_t N, int64_t K, int trans_a, int trans_b)
+{
+    return gemm_tc_supported(M, N, K) && (trans_a || trans_b) && (!trans_a || M % 8 == 0);
+}
+
+template <int TA, int TB>
+static dl4s_status run_gemm_tc_trans(DeviceState *st, const CUtensorMap &ta, const CUtensorMap &tb, const GemmTcParams &p, bool wide)
+{
+    if (wide) return run_gemm_tc_inst2<256, EPI_NONE, OUT_F32, 0, TA, TB>(st, ta, tb, p, "k_gemm_tc.transposed");
+    return run_gemm_tc_inst2<128, EPI_NONE, OUT_F32, 0, TA, TB>(st, ta, tb, p, "k_gemm_tc.transposed");
+}
+
+dl4s_status launch_gemm_tc_trans(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K,
+                                 int trans_a, int trans_b, void *scratch, size_t scratch_bytes)
+{
+    DL4S_REQUIRE(gemm_tc_trans_supported(M, N, K, trans_a, trans_b), "shape not supported by the transposed tensor-core gemm");
+    DL4S_REQUIRE(scratch && scratch_bytes >= gemm_tc_scratch_bytes(M, N, K, 0), "scratch too small");
+    DL4S_REQUIRE(c && ((uintptr_t)c & 15) == 0, "C must be 16-byte aligned");
+    __half *ah = (__half *)scratch;
+    __half *bh = (__half *)((char *)scratch + align_up((size_t)(M * K) * 2, 1024));
+    DL4S_TRY(launch_f32_to_f16(st, a, ah, M * K));
+    DL4S_TRY(launch_f32_to_f16(st, b, bh, K * N));
+    const bool wide = gemm_tc_wide_tiles(N);
+    CUtensorMap ta, tb;
+    if (trans_a)   // stored [K][M]: boxes of 64 m x 64 k-rows
+        DL4S_TRY(make_tmap_f16(&ta, ah, (uint64_t)M, (uint64_t)K, 0, (uint64_t)M * 2, 0, 64, GK));
+    else
+        DL4S_TRY(make_tmap_f16(&ta, ah, (uint64_t)K, (uint64_t)M, 1, (uint64_t)K * 2, (uint64_t)(M * K) * 2, GK, GM));
+    if (trans_b)   // stored [N][K]: one box of BN rows x 64 k
+        DL4S_TRY(make_tmap_f16(&tb, bh, (uint64_t)K, (uint64_t)N, 0, (uint64_t)K * 2, 0, GK, wide ? 256 : 128));
+    else
+        DL4S_TRY(make_tmap_f16(&tb, bh, (uint64_t)N, (uint64_t)K, 0, (uint64_t)N * 2, 0, 64, GK));
+    GemmTcParams p = {};
+    p.c = c;
+    p.M = M; p.N = N; p.K = K;
+    p.a_kc = (int)K;
+    p.a_groups = 1;
+    p.epilogue = EPI_NONE;
+    p.out_mode = OUT_F32;
+    p.status = st->status_word;
+    p.S = 1; p.H = 1;
+    for (int i = 0; i < 3; ++i) { p.part_d[i] = 32; p.part_scale[i] = 1.f; }
+    if (trans_a && trans_b) return run_gemm_tc_trans<1, 1>(st, ta, tb, p, wide);
+    if (trans_a) return run_gemm_tc_trans<1, 0>(st, ta, tb, p, wide);
+    return run_gemm_tc_trans<0, 1>(st, ta, tb, p, wide);
 }
 
 }  // namespace dl4s

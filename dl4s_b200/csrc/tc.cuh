@@ -14,6 +14,11 @@ dl4s_status launch_gemm_tc(DeviceState *st, const float *a, const float *b, floa
                            int epilogue, const float *bias, const float *residual, void *scratch, size_t scratch_bytes,
                            int split = 0, const DropoutSpec *drop = nullptr);
 
+// C = op(A) op(B) with A stored [K, M] (trans_a) and/or B stored [N, K] (trans_b): the products of a matmul's backward.
+bool gemm_tc_trans_supported(int64_t M, int64_t N, int64_t K, int trans_a, int trans_b);
+dl4s_status launch_gemm_tc_trans(DeviceState *st, const float *a, const float *b, float *c, int64_t M, int64_t N, int64_t K,
+                                 int trans_a, int trans_b, void *scratch, size_t scratch_bytes);
+
 // The same product with operands that are already half ([M,K] and [K,N], 16-byte aligned)
 // and a choice of output: fp32 [M,N], half [M,N], or half scattered head-major into up to
 // three tensors [B,H,S,d] (rows are m = b*S + s; used by the fused q/k/v projection).

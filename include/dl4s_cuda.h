@@ -228,7 +228,9 @@ dl4s_status dl4s_cuda_band(const float *d_src, int64_t rows, int64_t cols, int32
                            int32_t above, int32_t has_above, float *d_result);                      /* :233 */
 /* gemm: C = alpha*op(A)*op(B) + beta*C, row-major, A stored [M,K] ([K,M] when
  * trans_a), B stored [K,N] ([N,K] when trans_b). Engine.swift:225;
- * CPUFloat.swift:263-292. `precision` selects FFMA or tensor cores. */
+ * CPUFloat.swift:263-292. `precision` selects FFMA or tensor cores: the tensor-core kernels take alpha = 1, beta = 0,
+ * M >= 128 and N, K multiples of 64, with or without transposed operands (the products of a matmul's backward,
+ * Tensor/Operators/Matrix.swift:139-173: dA = dC B^T, dB = A^T dC); other calls run on the fp32 kernel. */
 dl4s_status dl4s_cuda_gemm(const float *d_a, const float *d_b, float *d_c, int64_t M, int64_t N, int64_t K,
                            float alpha, float beta, int32_t trans_a, int32_t trans_b, int32_t precision);
 
@@ -319,6 +321,13 @@ dl4s_status dl4s_cuda_sdpa_decode_noalloc(const float *d_q, const float *d_k, co
  * MultiHeadAttention.swift:123 and PointwiseFeedForward.swift:79). */
 dl4s_status dl4s_cuda_layernorm(const float *d_x, const float *d_residual, int64_t outer, int64_t rows, int64_t D,
                                 const float *d_scale, const float *d_shift, float *d_out);
+
+/* Backward of dl4s_cuda_layernorm: the gradients DL4S's autograd obtains by chaining the backward closures of the
+ * primitives LayerNorm.callAsFunction is written with (LayerNorm.swift:62-77; Reduce.swift:87-110), in closed form.
+ * d_x is the layer's input (x + residual of the forward call), d_dy the upstream gradient, both [outer, rows, D];
+ * d_dx [outer, rows, D] (also the gradient of the residual); d_dscale, d_dshift [D] may both be NULL. fp32. */
+dl4s_status dl4s_cuda_layernorm_backward(const float *d_x, const float *d_dy, int64_t outer, int64_t rows, int64_t D,
+                                         const float *d_scale, float *d_dx, float *d_dscale, float *d_dshift);
 
 /* MultiHeadAttention.callAsFunction (NN/Models/Transformer/MultiHeadAttention.swift:97-127),
  * dropout inactive: out = LayerNorm_{per batch element over Sq x D}(

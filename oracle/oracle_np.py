@@ -107,3 +107,19 @@ def sdpa_backward(q, k, v, dout, mask=None, temperature=None, dtype=np.float64):
     dp = dout @ np.swapaxes(v, -1, -2)
     ds = p * (dp - (dp * p).sum(axis=-1, keepdims=True))
     return (ds @ k) / t, np.swapaxes(ds, -1, -2) @ (q / t), np.swapaxes(p, -1, -2) @ dout
+
+
+def layernorm_backward(x, dy, scale, dtype=np.float64):
+    """Closed-form gradients of layernorm() above with respect to x, scale and shift (float64 cross-check, pinned by
+    finite differences in tests/test_oracle.py)."""
+    x, dy, scale = (np.asarray(a, dtype) for a in (x, dy, scale))
+    axes = tuple(range(1, x.ndim))
+    n = np.prod(x.shape[1:])
+    m = x.mean(axis=axes, keepdims=True)
+    sd = np.sqrt((x * x).mean(axis=axes, keepdims=True) - m * m)
+    s = sd + dtype(1e-5)
+    xh = (x - m) / s
+    a = dy * scale
+    dx = (a - a.mean(axis=axes, keepdims=True) - xh * (a * xh).mean(axis=axes, keepdims=True) * (s / sd)) / s
+    red = tuple(range(x.ndim - 1))
+    return dx, (dy * xh).sum(axis=red), dy.sum(axis=red)

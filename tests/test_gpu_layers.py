@@ -473,3 +473,26 @@ def test_log_softmax_rows_in_place_and_ragged(dev, oracle):
         # values of O(20); a sum over 32000 fp32 terms carries ~1e-5 RELATIVE error in either order of summation (the
         # CPU engine adds them one after the other), so the bound is relative to the largest |value|
         assert_fp32_rel(t.numpy(), oracle.log_softmax_rows(x), f"log-softmax {rows} x {n}")
+
+
+def test_layernorm_backward(dev):
+    """dx, dscale, dshift of DL4S's LayerNorm against the float64 closed form (itself pinned by finite differences
+    in the CPU tier), for both flavours: statistics per batch element over [rows, D] and per row."""
+    from dl4s_b200._lib import c_vp, call
+    from oracle import oracle_np as ON
+    from util import assert_fp32_rel
+    rng = np.random.default_rng(91)
+    for shape in ((3, 40, 64), (5, 1, 512), (2, 128, 512)):
+        outer, rows, D = shape
+        x = rng.standard_normal(shape, dtype=np.float32) * 2 + 0.5
+        dy = rng.standard_normal(shape, dtype=np.float32)
+        g = (1 + 0.2 * rng.standard_normal(D)).astype(np.float32)
+        tx, tdy, tg = dev.tensor(x), dev.tensor(dy), dev.tensor(g)
+        dx, dg, db = (dev.CUDA.Memory.allocateBuffer(s) for s in (shape, (D,), (D,)))
+        call("dl4s_cuda_layernorm_backward", c_vp(tx.ptr), c_vp(tdy.ptr), outer, rows, D, c_vp(tg.ptr), c_vp(dx.ptr), c_vp(dg.ptr),
+             c_vp(db.ptr))
+        wx, wg, wb = ON.layernorm_backward(x, dy, g)
+        assert_fp32(dx.numpy(), wx, f"dx {shape}")
+        assert_fp32_rel(dg.numpy(), wg, f"dscale {shape}")      # sums over up to 256 rows: relative to their size
+        assert_fp32_rel(db.numpy(), wb, f"dshift {shape}")
+    assert dev.device_status() == 0

@@ -284,3 +284,27 @@ def test_bounded_wait_runs_out_and_is_reported(dev):
     want = A.astype(np.float16).astype(np.float64) @ B.astype(np.float16).astype(np.float64)
     assert np.abs(out.numpy() - want).max() <= 1e-3
     assert dev.device_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K,ta,tb", [(256, 128, 64, True, False), (256, 128, 64, False, True), (1000, 512, 256, True, True),
+                                         (1000, 512, 256, False, True), (512, 2048, 16384 // 32, True, False), (4096 + 80, 192, 320, False, True)])
+def test_gemm_tensor_core_transposed(dev, M, N, K, ta, tb):
+    """The products of a matmul's backward (dA = dC B^T, dB = A^T dC, Matrix.swift:139-173) on the tensor cores:
+    operands stored transposed, against the float64 product of the half-rounded operands."""
+    from dl4s_b200 import PREC_F16
+    E = dev.CUDA.Engine
+    rng = np.random.default_rng(M + 7 * N + K)
+    A = rng.standard_normal((M, K)).astype(np.float32)
+    B = (rng.standard_normal((K, N)) * 0.1).astype(np.float32)
+    a = np.ascontiguousarray(A.T) if ta else A
+    b = np.ascontiguousarray(B.T) if tb else B
+    out = dev.CUDA.Memory.allocateBuffer((M, N))
+    dev.profile_begin()
+    E.gemm(up(dev, a), up(dev, b), out, transposeFirst=ta, transposeSecond=tb, precision=PREC_F16)
+    prof = dev.profile_end()
+    assert "k_gemm_tc.transposed" in prof, sorted(prof)
+    got = out.numpy()
+    want = A.astype(np.float16).astype(np.float64) @ B.astype(np.float16).astype(np.float64)
+    err = np.abs(got - want).max()
+    assert err <= 2e-5 * max(1.0, np.abs(want).max()) * np.sqrt(K), f"max error {err} vs the product of the rounded operands"
+    assert dev.device_status() == 0

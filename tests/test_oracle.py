@@ -218,3 +218,31 @@ def test_sdpa_backward_matches_finite_differences_and_float64(oracle):
             assert abs(fd - grad[idx]) <= 1e-6 * max(1.0, abs(fd)), (idx, fd, grad[idx])
     # keys a sequence cannot see get no gradient
     assert np.abs(dk[1, :, 4:]).max() == 0.0 and np.abs(dv[1, :, 4:]).max() == 0.0
+
+
+def test_layernorm_backward_matches_finite_differences():
+    """The closed form the device kernel implements, against central differences of the float64 forward."""
+    from oracle import oracle_np as ON
+    rng = np.random.default_rng(33)
+    for shape in ((3, 5, 8), (4, 6)):
+        x = rng.standard_normal(shape)
+        dy = rng.standard_normal(shape)
+        g = 1 + 0.3 * rng.standard_normal(shape[-1])
+        b = 0.3 * rng.standard_normal(shape[-1])
+        dx, dg, db = ON.layernorm_backward(x, dy, g)
+        loss = lambda xx, gg, bb: float((ON.layernorm(xx, gg, bb) * dy).sum())
+        eps = 1e-6
+        for idx in [tuple(rng.integers(0, s) for s in shape) for _ in range(6)]:
+            xp, xm = x.copy(), x.copy()
+            xp[idx] += eps
+            xm[idx] -= eps
+            assert abs((loss(xp, g, b) - loss(xm, g, b)) / (2 * eps) - dx[idx]) < 1e-6
+        for c in range(shape[-1]):
+            gp, gm = g.copy(), g.copy()
+            gp[c] += eps
+            gm[c] -= eps
+            assert abs((loss(x, gp, b) - loss(x, gm, b)) / (2 * eps) - dg[c]) < 1e-6
+            bp, bm = b.copy(), b.copy()
+            bp[c] += eps
+            bm[c] -= eps
+            assert abs((loss(x, g, bp) - loss(x, g, bm)) / (2 * eps) - db[c]) < 1e-6

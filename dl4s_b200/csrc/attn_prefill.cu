@@ -106,11 +106,6 @@ __device__ __forceinline__ float fast_exp2(float x)
     return y;
 }
 
-#ifndef DL4S_ATTN_POLY_OF_4
-#define DL4S_ATTN_POLY_OF_4 0
-#endif
-constexpr int kPolyOf4 = DL4S_ATTN_POLY_OF_4;   // pairs out of every 4 whose 2^x runs on the FMA pipe
-
 __device__ __forceinline__ float max3(float a, float b, float c)
 {
     float d;
@@ -134,36 +129,6 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
     asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
-{
-    uint64_t r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
-// 2^x for a pair, x <= ~8: round to the nearest integer n with the 1.5*2^23 trick, evaluate a
-// cubic minimax polynomial of 2^f on f = x - n in [-0.5, 0.5] (relative error 7.5e-5, well
-// below the 4.9e-4 of the half rounding that follows) and add n to the exponent field.
-__device__ __forceinline__ void exp2_poly2(uint64_t x2, float &p0, float &p1)
-{
-    float x0, x1;
-    unpack2(x2, x0, x1);
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
-    const uint64_t xc = pack2(x0, x1);
-    const uint64_t magic = pack2(12582912.0f, 12582912.0f);
-    const uint64_t t2 = add2(xc, magic);
-    const uint64_t n2 = add2(t2, pack2(-12582912.0f, -12582912.0f));
-    const uint64_t f2 = fma2(n2, pack2(-1.0f, -1.0f), xc);
-    uint64_t q = fma2(f2, pack2(0.0551716685f, 0.0551716685f), pack2(0.2426111251f, 0.2426111251f));
-    q = fma2(q, f2, pack2(0.6932609677f, 0.6932609677f));
-    q = fma2(q, f2, pack2(0.9999280572f, 0.9999280572f));
-    float q0, q1, t0, t1;
-    unpack2(q, q0, q1);
-    unpack2(t2, t0, t1);
-    p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
-    p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
-}
-
 __device__ __forceinline__ uint32_t pack_half2(float a, float b)
 {
     __half2 h = __floats2half2_rn(a, b);   // a in the low half: element 2c of the row
@@ -414,8 +379,7 @@ __global__ void __launch_bounds__(at_threads(NT), NT == 2 ? 1 : 2) k_attn_prefil
                 }
             }
             // p = 2^(s - m_used), packed as halves over the first 64 columns of the score tile.
-            // Pairs of columns go through packed fp32x2 arithmetic; kPolyOf4 of every 4 pairs
-            // evaluate 2^x with a cubic on the FMA pipe instead of the exp2 unit.
+            // Pairs of columns go through packed fp32x2 arithmetic.
             const uint64_t negm2 = pack2(-m_used, -m_used);
             uint64_t acc0 = pack2(0.f, 0.f), acc1 = acc0;
 #pragma unroll
@@ -424,15 +388,10 @@ __global__ void __launch_bounds__(at_threads(NT), NT == 2 ? 1 : 2) k_attn_prefil
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     uint64_t x2 = add2(pack2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), negm2);
-                    float p0, p1;
-                    if ((i & 3) < kPolyOf4) {
-                        exp2_poly2(x2, p0, p1);
-                    } else {
-                        float x0, x1;
-                        unpack2(x2, x0, x1);
-                        p0 = fast_exp2(x0);
-                        p1 = fast_exp2(x1);
-                    }
+                    float p0, p1, x0, x1;
+                    unpack2(x2, x0, x1);
+                    p0 = fast_exp2(x0);
+                    p1 = fast_exp2(x1);
                     if (i & 1) acc1 = add2(acc1, pack2(p0, p1));
                     else acc0 = add2(acc0, pack2(p0, p1));
                     pk[i] = pack_half2(p0, p1);

@@ -675,28 +675,8 @@ size_t gemm_tc_scratch_bytes(int64_t M, int64_t N, int64_t K, int split)
     return align_up((size_t)(M * K) * 2, 1024) + align_up((size_t)(K * N) * (split ? 4 : 2), 1024);
 }
 
-// DL4S_GEMM_PAIRS=0 in the environment selects the single-CTA kernel everywhere (for comparisons).
-static bool gemm_tc_pairs_enabled()
-{
-    static int v = -1;
-    if (v < 0) {
-        const char *e = getenv("DL4S_GEMM_PAIRS");
-        v = (e && e[0] == '0') ? 0 : 1;
-    }
-    return v == 1;
-}
-
-// Shortest main loop (K) that uses pairs; DL4S_GEMM_PAIR_MIN_K overrides it for measurements.
-static int64_t gemm_tc_pair_min_k()
-{
-    static int64_t v = -1;
-    if (v < 0) {
-        const char *e = getenv("DL4S_GEMM_PAIR_MIN_K");
-        v = e ? atoll(e) : 1024;
-        if (v < GK) v = GK;
-    }
-    return v;
-}
+// Shortest main loop (K) that uses two-CTA tiles.
+constexpr int64_t kPairMinK = 1024;
 
 template <int BN, int EPI, int OUT, int PAIR, int TA = 0, int TB = 0>
 static dl4s_status run_gemm_tc_inst2(DeviceState *st, const CUtensorMap &ta, const CUtensorMap &tb, GemmTcParams p, const char *name)
@@ -734,7 +714,7 @@ static dl4s_status run_gemm_tc_inst2(DeviceState *st, const CUtensorMap &ta, con
 template <int BN, int EPI, int OUT>
 static dl4s_status run_gemm_tc_inst(DeviceState *st, const CUtensorMap &ta, const CUtensorMap &tb, GemmTcParams p, const char *name)
 {
-    if (BN == 256 && p.M >= 2 * GM && p.K >= gemm_tc_pair_min_k() && gemm_tc_pairs_enabled())
+    if (BN == 256 && p.M >= 2 * GM && p.K >= kPairMinK)
         return run_gemm_tc_inst2<BN, EPI, OUT, (BN == 256)>(st, ta, tb, p, name);
     return run_gemm_tc_inst2<BN, EPI, OUT, 0>(st, ta, tb, p, name);
 }

@@ -372,6 +372,14 @@ dl4s_status dl4s_cuda_mha_forward_sharded(const float *d_x, int64_t B, int64_t S
                                             d_out + plan[i].out0 * S * D, precision, half, world, Bc * S * C);
     };
     c.last_chunks = world > 1 ? nchunks : 0;
+    // While gathers are in flight their kernel holds some SMs: the products take their tiles from the device-wide
+    // counter, so a CTA that starts late behind it simply takes fewer.
+    struct DynamicTiles {
+        DeviceState *st;
+        int saved;
+        DynamicTiles(DeviceState *s, int on) : st(s), saved(s->dynamic_tiles) { st->dynamic_tiles = on; }
+        ~DynamicTiles() { st->dynamic_tiles = saved; }
+    } dynamic_tiles(st, world > 1 && nchunks > 1);
     int pending = -1;
     for (int i = 0; i < nchunks; ++i) {
         DL4S_TRY(heads(i));

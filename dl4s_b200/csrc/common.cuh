@@ -48,6 +48,10 @@ struct DeviceState {
     // lives a buffer that has to grow is retired (kept allocated) instead of freed; the retired buffers go
     // when the last graph is destroyed.
     int live_graphs = 0;
+    // Tensor-core GEMMs take their tiles from a device-wide counter (1) instead of a fixed round-robin schedule (0).
+    // Set while the launches share the SMs with a collective's kernel, where a CTA that starts late should take
+    // fewer tiles; otherwise the fixed schedule saves the counter's round trips.
+    int dynamic_tiles = 0;
     void *retired[kMaxRetired] = {};
     int n_retired = 0;
     // Sinusoidal positional-encoding table [pe_rows, pe_dim], built on first use and kept.

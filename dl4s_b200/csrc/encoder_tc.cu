@@ -29,6 +29,12 @@
 
 namespace dl4s {
 
+// Two-half weights in the q/k/v projection: only the value columns take the remainder W_lo. The rounding of Wq and Wk
+// moves the scores before a softmax that averages over hundreds of keys and is not visible in the encoder's output
+// (the 6-layer configuration's error is the same with and without their remainders), while Wv's goes straight into
+// the residual stream.
+constexpr bool kSplitValueOnly = true;
+
 // fp32 [rows, na] | [rows, nb] | [rows, nc] -> half [rows, na+nb+nc] (b, c optional);
 // lo_off != 0: the half-rounded remainders go `lo_off` elements further (the split form).
 __global__ void __launch_bounds__(256) k_concat_cols_f16(const float *__restrict__ a, int na, const float *__restrict__ b, int nb,
@@ -229,7 +235,8 @@ static dl4s_status mha_tc_run(DeviceState *st, const float *xq, const float *xk,
         o.part_ptr[0] = m.qh; o.part_ptr[1] = m.kh; o.part_ptr[2] = m.vh;
         o.part_d[0] = (int)dk; o.part_d[1] = (int)dk; o.part_d[2] = (int)dv;
         o.part_scale[0] = q_scale;
-        DL4S_TRY(launch_gemm_tc_h(st, m.xq_h, m.wqkv_h, B * Sq, 2 * Nq + Nv, D, EPI_NONE, nullptr, nullptr, o, 1, 0, split));
+        DL4S_TRY(launch_gemm_tc_h(st, m.xq_h, m.wqkv_h, B * Sq, 2 * Nq + Nv, D, EPI_NONE, nullptr, nullptr, o, 1, 0, split, nullptr,
+                                  kSplitValueOnly ? 2 * Nq : 0));
     } else {
         // Distinct query / key / value inputs: three products against the column blocks of the
         // concatenated weights are not contiguous operands, so the weights are taken apart again.
@@ -350,7 +357,8 @@ dl4s_status mha_heads_self_tc(DeviceState *st, const float *x, int64_t B, int64_
     o.part_ptr[0] = qh; o.part_ptr[1] = kh; o.part_ptr[2] = vh;
     o.part_d[0] = (int)dk; o.part_d[1] = (int)dk; o.part_d[2] = (int)dv;
     o.part_scale[0] = attn_prefill_tc_q_scale(1.0f / sqrtf((float)dk));
-    DL4S_TRY(launch_gemm_tc_h(st, xh, w, B * S, 2 * Nq + Nv, D, EPI_NONE, nullptr, nullptr, o, 1, 0, split));
+    DL4S_TRY(launch_gemm_tc_h(st, xh, w, B * S, 2 * Nq + Nv, D, EPI_NONE, nullptr, nullptr, o, 1, 0, split, nullptr,
+                              kSplitValueOnly ? 2 * Nq : 0));
     return launch_attn_prefill_tc_h(st, qh, kh, vh, out, strides_bshd(H, S, dv), out_half, B, H, S, S, dk, mask);
 }
 

@@ -6,10 +6,7 @@
 // Operands are rounded to half once by a conversion pass (A [M,K], B [K,N]); the
 // MMA is tcgen05.mma kind::f16 with fp32 accumulation in tensor memory.
 // One persistent CTA per SM works through 128 x BN output tiles:
-//   warp 0    TMA producer: takes the next tile from a device-wide counter (so a
-//             CTA that starts late, e.g. behind a collective's kernel on its SM,
-//             simply takes fewer tiles), publishes it to the other warps through a
-//             small ring, and loads A [128 rows x 64 k] (K-major) and B
+//   warp 0    TMA producer: loads A [128 rows x 64 k] (K-major) and B
 //             [64 k-rows x BN] (N contiguous = MN-major, BN/64 boxes) into a
 //             ring of 192 KB (4 stages of 48 KB for 256-column tiles, 6 of 32 KB for
 //             128-column tiles and for each CTA of a pair), 128-byte swizzle;
@@ -18,26 +15,38 @@
 //             overlaps the epilogue of the previous one;
 //   warps 2.. epilogue (8 or 16 warps by flavour): 16-lane x 256-bit tensor-memory
 //             loads, 32 columns at a time, whose register layout lets four lanes
-//             store 32 contiguous bytes of a row (whole sectors) straight from
-//             registers; fused bias / GeLU / residual / LayerNorm sums.
+//             store whole sectors of a row straight from registers; fused bias /
+//             GeLU / residual / LayerNorm sums.
+// Tile schedule. By default worker w (a CTA, or a pair) takes tiles w, w + workers, ...: every role works the
+// sequence out by itself and nothing is handed around. While a collective's kernel shares the SMs
+// (DeviceState::dynamic_tiles) the tiles after the first come from a device-wide counter instead, so a CTA that
+// starts late behind that kernel simply takes fewer; the producer then publishes each tile to the other warps (and
+// the other CTA of a pair) through a small ring, one tile ahead of its loads.
 // Tiles are numbered so that the ~148 tiles in flight form a block of 16 tile rows
 // x ~9 tile columns: their A and B panels (tens of MB) stay in L2, where a
 // column-major walk would stream all of A from HBM once per tile column.
 // What bounds the single-CTA main loop: shared-memory bandwidth. Per k-block TMA writes 48 KB of operands and
 // the tensor core reads them once (A 16 KB + B 32 KB): 96 KB against 128 bytes per clock = 750 cycles where the
-// MMAs alone need 512. clock64 stamps around the waits showed ~960 cycles per k-block (7700 per 128 x 256 tile
-// at K = 512, the same ~50 B/clk of operands per SM the kernel shows at 8192^3) while the epilogue still turned
-// the accumulators through shared memory (another 256 KB per tile, and ~2400 cycles per 32 x 32 block under
-// that load); with the epilogue out of shared memory the q/k/v projection went from 0.224 to 0.210 ms and
-// feed-forward 1 from 0.283 to 0.269 ms per encoder step. Fewer operand bytes per flop is what helps further
-// (the two-CTA tiles below: 64 KB of shared-memory traffic per k-block and CTA), once the main loop is long
-// enough to pay for the pair's hand-offs.
+// MMAs alone need 512; clock64 stamps show 750 cycles per k-block in the steady state. The two-CTA tiles below
+// need 64 KB per k-block and CTA and run at 520-580.
+// What bounds a tile at K = 512 (8 k-blocks) is not the main loop alone. With two accumulators the MMAs of tile
+// i+2 wait for the drain of tile i, so a tile costs (main loop + hand-offs + time the accumulator is held) / 2.
+// Three things shortened that chain (clock64 stamps per role, first pair of CTAs):
+//   * hand-offs that publish no memory are relaxed arrives: a release arrive after the epilogue's global stores
+//     (or after the producer's counter atomic) waits until those have been performed, 1000-3400 cycles that the
+//     MMA thread then spent waiting for an accumulator or for a tile's first operands;
+//   * the half-output flavours read their whole share of the accumulator into registers, hand it back, and only
+//     then convert and store (the accumulator is held ~1000 cycles instead of ~5000);
+//   * the first tile's loads are issued before anything else the producer does.
+// After that the half-output flavours at K = 512 are bound by the epilogue warps' instruction issue (~1000
+// instructions per warp and tile, issue slots 46 % busy with 4 warps per scheduler, ~5000-5500 cycles per tile
+// against a 4300-cycle pair main loop): single-CTA and two-CTA tiles then run at the same rate, and short
+// products keep the single-CTA kernel.
 // Every mbarrier wait is bounded; on expiry the kernel sets the device status
 // word and unwinds through the common exit, which frees the tensor memory.
 #include "tc.cuh"
 #include "tc_device.cuh"
 
-#include <cstdlib>
 
 namespace dl4s {
 
@@ -49,9 +58,9 @@ constexpr int GK = 64;           // k per stage (one 128-byte swizzle row of hal
 // Measured on the encoder's K = 512 products (per step): 16 warps (96 registers each) against 8 for
 // feed-forward 1 (bias + GeLU, 2 MUFU per element) 0.269 vs 0.310 ms, for the q/k/v projection 0.210 either
 // way, for the flavours that add a residual 0.448 vs 0.444 ms: those keep 8 warps, whose registers hold the
-// prefetched residual values, and so do the two-CTA tiles, whose long main loop hides the epilogue anyway.
+// prefetched residual values. Single-CTA and two-CTA tiles use the same count.
 __host__ __device__ constexpr bool epi_has_residual(int epi) { return epi == EPI_BIAS_RESIDUAL || epi == EPI_RESIDUAL || epi == EPI_RESIDUAL_STATS; }
-__host__ __device__ constexpr int epi_parts(int epi, int pair) { return (epi_has_residual(epi) || pair) ? 2 : 4; }
+__host__ __device__ constexpr int epi_parts(int epi, int pair) { return epi_has_residual(epi) ? 2 : 4; }
 __host__ __device__ constexpr int gemm_threads(int epi, int pair) { return 64 + 32 * 4 * epi_parts(epi, pair); }   // warp 0 TMA, warp 1 MMA, then the epilogue warps
 
 // DL4S's GeLU, t * sigmoid(1.702 t) with sigmoid(y) = 0.5 tanh(y/2) + 0.5 (Unary.swift:184-186,
@@ -157,6 +166,9 @@ struct GemmTcParams {
     int32_t *status;
     double *ln_stats;        // EPI_RESIDUAL_STATS: partial sums per (32 rows, half tile), see tc.cuh
     int32_t *tile_counter;   // {tiles handed out beyond the first gridDim.x, CTAs done}
+    int dynamic_tiles;       // 0: worker w takes tiles w, w + workers, ... ; 1: tiles after the first come from the counter
+    int lo_from_tn;          // split B: tile columns below this one use W_hi alone (kblocks_hi k-blocks), the others hi + lo
+    int kblocks_hi;
     int a_kc;                // A's k extent per column group (K when A is one plain matrix)
     DropoutSpec drop;        // residual flavours: dropout of the product (+ bias) before the residual is added
     int test_skip_kb;        // -1; test only: the k-block of a CTA's first tile whose loads are left out
@@ -256,6 +268,13 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
 
     const int num_tiles = p.tiles_m * p.tiles_n;
     const int kblocks = (int)(p.K / GK);
+    // k-blocks of one tile: all of them, or the first half (W_hi alone) for the columns that do not take the remainder
+    auto tile_kblocks = [&](int tile) -> int {
+        if (p.lo_from_tn == 0) return kblocks;
+        int tm, tn;
+        tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+        return tn < p.lo_from_tn ? p.kblocks_hi : kblocks;
+    };
 
     if (warp == 0) {
         if (elect_one()) {
@@ -279,46 +298,28 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                 }
                 return true;
             };
-            int cur = blockIdx.x / CTAS, nxt = 0;
-            if (leader) {
-                nxt = workers + atomicAdd(p.tile_counter, 1);
-                ok = publish(0, cur);
-            }
-            for (int it = 0; ok; ++it) {
-                const int slot = it % G_TILE_RING;
-                int this_tile;
-                if (leader) {
-                    if (cur >= num_tiles) break;   // the end marker has been published
-                    const int nxt2 = workers + atomicAdd(p.tile_counter, 1);
-                    if (!publish(it + 1, nxt)) break;
-                    this_tile = cur;
-                    cur = nxt;
-                    nxt = nxt2;
-                } else {
-                    if (!mbar_wait_cluster(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
-                    this_tile = tile_ring[slot];
-                    mbar_arrive_remote(&tile_empty[slot], 0);
-                    if (this_tile >= num_tiles) break;
-                }
+            int kx = 0, kz = 0;   // A is [groups][rows][a_kc]: k = kz * a_kc + kx
+            // Loads of k-blocks [kb0, kb1) of one tile; false after a wait that gave up.
+            auto load_kblocks = [&](int this_tile, int it, int kb0, int kb1) -> bool {
                 int tm, tn;
                 tile_coords(this_tile, p.tiles_m, p.tiles_n, tm, tn);
                 const int row0 = (tm * CTAS + (int)rank) * GM, col0 = tn * BN + (int)rank * BN_CTA;
-                int kx = 0, kz = 0;   // A is [groups][rows][a_kc]: k = kz * a_kc + kx
-                for (int kb = 0; kb < kblocks; ++kb) {
-                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.wait_polls)) { ok = false; break; }
+                if (kb0 == 0) { kx = 0; kz = 0; }
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag, p.wait_polls)) return false;
                     uint8_t *sa = smem + stage * STAGE_BYTES;
                     if (!PAIR && it == 0 && kb == p.test_skip_kb) {
                         // Injected fault (dl4s_cuda_inject_failure): this stage is never filled, so the MMA thread's
                         // bounded wait on it runs out and the CTA unwinds through the common exit.
                     } else if (PAIR) {
                         // both CTAs' bytes are counted on the leader's barrier
-                        if (leader) mbar_expect_tx(&full_bar[stage], STAGE_BYTES * CTAS);
+                        if (leader) mbar_expect_tx_relaxed(&full_bar[stage], STAGE_BYTES * CTAS);
                         tma_load_3d_pair(sa, &tmap_a, &full_bar[stage], kx, row0, kz);
 #pragma unroll
                         for (int nb = 0; nb < BN_CTA / 64; ++nb)
                             tma_load_2d_pair(sa + A_BYTES + nb * B_BLOCK, &tmap_b, &full_bar[stage], col0 + nb * 64, kb * GK);
                     } else {
-                        mbar_expect_tx(&full_bar[stage], STAGE_BYTES);
+                        mbar_expect_tx_relaxed(&full_bar[stage], STAGE_BYTES);
                         if (TA) {
 #pragma unroll
                             for (int mb = 0; mb < GM / 64; ++mb)
@@ -338,22 +339,76 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                     kx += GK;
                     if (kx == p.a_kc) { kx = 0; if (++kz == p.a_groups) kz = 0; }
                 }
+                return true;
+            };
+            // Order within a tile: publish the next tile (a release arrive), THEN ask the counter for the one after
+            // it, then load. A release arrive waits for the thread's outstanding atomic, so an atomic issued before
+            // the publish would put its whole round trip (~1000-3000 cycles) between two tiles' loads; issued after
+            // it, the round trip runs under this tile's loads, whose barrier operations are relaxed.
+            int cur = blockIdx.x / CTAS, nxt = 0;
+            int it_begin = 0;
+            if (!p.dynamic_tiles) {
+                // Fixed schedule: every role of every CTA works the tile sequence out by itself.
+                for (int it = 0, t = cur; ok && t < num_tiles; ++it, t += workers) ok = load_kblocks(t, it, 0, tile_kblocks(t));
+                ok = false;   // done: skip the counter-driven loop below
+            } else if (leader) {
+                const int a1 = atomicAdd(p.tile_counter, 1);      // tile 1 of this CTA (pair)
+                ok = publish(0, cur);                             // waits for a1: nothing else to do yet
+                if (ok) {
+                    // the ring is empty: its first stages are requested before the counter's answer is needed
+                    const int kbt = tile_kblocks(cur);
+                    const int first = kbt < G_STAGES ? kbt : G_STAGES;
+                    ok = load_kblocks(cur, 0, 0, first);
+                    nxt = workers + a1;
+                    if (ok) ok = publish(1, nxt);
+                    const int a2 = atomicAdd(p.tile_counter, 1);  // tile 2, needed when tile 1's loads begin
+                    if (ok) ok = load_kblocks(cur, 0, first, kbt);
+                    cur = nxt;
+                    nxt = workers + a2;
+                    it_begin = 1;
+                }
+            }
+            for (int it = it_begin; ok; ++it) {
+                const int slot = it % G_TILE_RING;
+                int this_tile;
+                if (leader) {
+                    if (cur >= num_tiles) break;   // the end marker has been published
+                    if (!publish(it + 1, nxt)) break;
+                    const int nxt2 = workers + atomicAdd(p.tile_counter, 1);
+                    this_tile = cur;
+                    cur = nxt;
+                    ok = load_kblocks(this_tile, it, 0, tile_kblocks(this_tile));
+                    nxt = nxt2;
+                } else {
+                    if (!mbar_wait_cluster(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
+                    this_tile = tile_ring[slot];
+                    if (this_tile >= num_tiles) break;             // the end marker's slot is never reused
+                    mbar_arrive_remote_relaxed(&tile_empty[slot], 0);   // issued after the branch on the value read
+                    ok = load_kblocks(this_tile, it, 0, tile_kblocks(this_tile));
+                }
             }
         }
     } else if (warp == 1) {
         if (leader && elect_one()) {
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
+            const int workers = (int)(gridDim.x / CTAS);
             for (int it = 0; ok; ++it) {
                 const int slot = it % G_TILE_RING;
-                if (!mbar_wait(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
-                const int tile = tile_ring[slot];
-                mbar_arrive(&tile_empty[slot]);
+                int tile;
+                if (!p.dynamic_tiles) {
+                    tile = (int)(blockIdx.x / CTAS) + it * workers;
+                } else {
+                    if (!mbar_wait(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
+                    tile = tile_ring[slot];
+                    mbar_arrive(&tile_empty[slot]);
+                }
                 if (tile >= num_tiles) break;
                 if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, p.wait_polls)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < kblocks; ++kb) {
+                const int kbt = tile_kblocks(tile);
+                for (int kb = 0; kb < kbt; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag, p.wait_polls)) { ok = false; break; }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + stage * STAGE_BYTES);
@@ -382,18 +437,26 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
         bool ok = true;
         for (int it = 0; ok; ++it) {
             const int slot = it % G_TILE_RING;
-            if (PAIR && !leader) {
-                if (!mbar_wait_cluster(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
+            int tile;
+            if (!p.dynamic_tiles) {
+                tile = (int)(blockIdx.x / CTAS) + it * (int)(gridDim.x / CTAS);
+                if (tile >= num_tiles) break;
             } else {
-                if (!mbar_wait(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
+                if (PAIR && !leader) {
+                    if (!mbar_wait_cluster(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
+                } else {
+                    if (!mbar_wait(&tile_full[slot], (it / G_TILE_RING) & 1, abort_flag, p.wait_polls)) break;
+                }
+                tile = tile_ring[slot];
+                if (tile >= num_tiles) break;   // the end marker's slot is never reused: no arrival needed
+                // Relaxed: the slot's value has been read (the branch above depends on it) and nothing this warp
+                // wrote is handed over; a release arrive here would wait for the previous tile's global stores.
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR && !leader) mbar_arrive_remote_relaxed(&tile_empty[slot], 0);
+                    else mbar_arrive_relaxed(&tile_empty[slot]);
+                }
             }
-            const int tile = tile_ring[slot];
-            __syncwarp();
-            if (lane == 0) {
-                if (PAIR && !leader) mbar_arrive_remote(&tile_empty[slot], 0);
-                else mbar_arrive(&tile_empty[slot]);
-            }
-            if (tile >= num_tiles) break;
             int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
             if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, p.wait_polls)) { ok = false; break; }
@@ -458,10 +521,12 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                 // The next 32 columns travel from tensor memory while this group is written out.
                 if (has_next) load_group(rnx, c0 + 32);
                 if (col0 >= p.N) return;   // N is a multiple of 64: a 32-column group is all in or all out
-                // Half outputs: two lanes that hold neighbouring column pairs swap one pair each, so that every lane
-                // stores 4 consecutive halves (8 bytes) and the four lanes of a row 32 contiguous bytes: whole
-                // sectors. ch = first of the 4 columns (within 8) this lane then stores.
-                const int ch = ((lane >> 1) & 1) * 4;
+                // Half outputs: the four lanes of a row hold, after conversion, one half2 at columns 8p + 2j (p = 0..3,
+                // j = lane % 4). A 4 x 4 transpose among them (two shuffle rounds) leaves lane j with the eight
+                // consecutive columns 8j .. 8j+7, one 16-byte store per row: a warp store then covers 8 rows x 64
+                // contiguous bytes, half as many store instructions (and line visits in the load/store unit) as
+                // 8-byte stores, which is what the epilogue's length was made of. ch = first column this lane stores.
+                const int ch = (lane & 3) * 8;
                 // Head-major output: the 32-column group lies inside one head of one part.
                 __half *part_base = nullptr;
                 int part_d = 1, head = 0, dcol = 0;
@@ -545,21 +610,47 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                         }
                     }
                     if (OUT != OUT_F32) {
-#pragma unroll
-                        for (int p2 = 0; p2 < 4; p2 += 2) {
-                            const uint32_t send = (lane & 1) ? h2[p2] : h2[p2 + 1];
-                            const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
-                            uint2 o;
-                            o.x = (lane & 1) ? recv : h2[p2];
-                            o.y = (lane & 1) ? h2[p2 + 1] : recv;
-                            if (row_ok) *reinterpret_cast<uint2 *>(hrow + (p2 + (lane & 1)) * 8) = o;
-                        }
+                        const bool odd = lane & 1, hi = lane & 2;
+                        const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? h2[0] : h2[1], 1);
+                        const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? h2[2] : h2[3], 1);
+                        const uint32_t a0 = odd ? r0 : h2[0], a1 = odd ? h2[1] : r0;
+                        const uint32_t a2 = odd ? r1 : h2[2], a3 = odd ? h2[3] : r1;
+                        const uint32_t q0 = __shfl_xor_sync(0xffffffffu, hi ? a0 : a2, 2);
+                        const uint32_t q1 = __shfl_xor_sync(0xffffffffu, hi ? a1 : a3, 2);
+                        uint4 o;
+                        o.x = hi ? q0 : a0; o.y = hi ? q1 : a1;
+                        o.z = hi ? a2 : q0; o.w = hi ? a3 : q1;
+                        if (row_ok) *reinterpret_cast<uint4 *>(hrow) = o;
                     }
                 }
             };
             uint32_t ra[32], rb[32];
-            if (!kHasResidual && G_EPI_PARTS == 2) {
-                // Two register sets take turns (no copies): BN/2 columns per warp are 2 or 4 groups.
+            constexpr int NG = BN / G_EPI_PARTS / 32;          // 32-column groups per warp
+            constexpr bool kEarlyRelease = !kHasResidual && NG <= 2;
+            auto release_acc = [&]() {
+                // The accumulator goes back to the MMA thread. Every tensor-memory load of this warp has completed
+                // (tcgen05.wait::ld) and is ordered before the arrive by the fence; the tile's global stores are
+                // nobody's business here, so the arrive is relaxed and does not wait for them.
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (PAIR && !leader) mbar_arrive_remote_relaxed(&acc_empty[acc], 0);
+                    else mbar_arrive_relaxed(&acc_empty[acc]);
+                }
+            };
+            if constexpr (kEarlyRelease) {
+                // The warp's whole share of the accumulator (64 columns of 32 rows = 64 registers per lane) is read
+                // first and the accumulator handed back before anything is converted or stored: with two
+                // accumulators the MMAs of tile i+2 wait for the drain of tile i, so the time an accumulator is held
+                // (not the length of the epilogue) is what the tile rate sees.
+                load_group(ra, c_begin);
+                if (NG == 2) load_group(rb, c_begin + 32);
+                tmem_wait_ld();
+                release_acc();
+                group(ra, rb, c_begin, false);
+                if (NG == 2) group(rb, ra, c_begin + 32, false);
+            } else if constexpr (!kHasResidual) {
+                // Two register sets take turns (no copies).
                 load_group(ra, c_begin);
 #pragma unroll 1
                 for (int c0 = c_begin; c0 < c_end; c0 += 64) {
@@ -589,12 +680,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                 }
             }
             if (OUT != OUT_F32 && half_overflow) atomicOr(p.status, kStatusHalfRange);
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if (PAIR && !leader) mbar_arrive_remote(&acc_empty[acc], 0);
-                else mbar_arrive(&acc_empty[acc]);
-            }
+            if (!kEarlyRelease) release_acc();
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
     }
@@ -697,6 +783,7 @@ static dl4s_status run_gemm_tc_inst2(DeviceState *st, const CUtensorMap &ta, con
     st->tile_counter_next = (st->tile_counter_next + 1) % kTileCounterSlots;
     p.test_skip_kb = -1;
     p.wait_polls = kWaitPolls;
+    p.dynamic_tiles = st->dynamic_tiles;
     if (!PAIR && !st->capturing && take_injected_failure(DL4S_INJECT_WAIT_TIMEOUT)) {
         p.test_skip_kb = p.K / GK > 1 ? 1 : 0;
         p.wait_polls = 1u << 16;
@@ -707,10 +794,9 @@ static dl4s_status run_gemm_tc_inst2(DeviceState *st, const CUtensorMap &ta, con
 }
 
 // Pairs of CTAs (one MMA over two SMs) for 256-column tiles with a long main loop (K >= 1024):
-// measured 1480 vs 1260 TFLOP/s at 8192^3. With K = 512 a tile has only 8 k-blocks: the pair's main loop
-// is then near the MMA rate (~580 cycles per k-block by clock64 stamps) but its MMA thread waits 30-55 % of
-// the time for an accumulator, and the encoder's q/k/v projection and feed-forward 1 run 13-20 % slower
-// as pairs (0.237 / 0.324 vs 0.210 / 0.269 ms per step), so short products keep the single-CTA kernel.
+// measured 1480 vs 1260 TFLOP/s at 8192^3. With K = 512 a tile has only 8 k-blocks and the epilogue warps set the
+// rate for either form (see the head of this file): the encoder's q/k/v projection and feed-forward 1 take
+// 0.222 / 0.270 ms per step as pairs and 0.220 / 0.278 ms as single CTAs, so short products keep the single-CTA kernel.
 template <int BN, int EPI, int OUT>
 static dl4s_status run_gemm_tc_inst(DeviceState *st, const CUtensorMap &ta, const CUtensorMap &tb, GemmTcParams p, const char *name)
 {
@@ -736,9 +822,9 @@ static dl4s_status run_gemm_tc(DeviceState *st, const CUtensorMap &ta, const CUt
             case EPI_BIAS: return run_gemm_tc_inst<BN, EPI_BIAS, OUT_F32>(st, ta, tb, p, "k_gemm_tc.bias_f32");
             case EPI_BIAS_GELU: return run_gemm_tc_inst<BN, EPI_BIAS_GELU, OUT_F32>(st, ta, tb, p, "k_gemm_tc.bias_f32");
             case EPI_BIAS_RELU: return run_gemm_tc_inst<BN, EPI_BIAS_RELU, OUT_F32>(st, ta, tb, p, "k_gemm_tc.bias_f32");
-            case EPI_BIAS_RESIDUAL: return run_gemm_tc_inst<BN, EPI_BIAS_RESIDUAL, OUT_F32>(st, ta, tb, p, "k_gemm_tc.residual_f32");
+            case EPI_BIAS_RESIDUAL: return run_gemm_tc_inst<BN, EPI_BIAS_RESIDUAL, OUT_F32>(st, ta, tb, p, "k_gemm_tc.bias_residual_f32");
             case EPI_RESIDUAL: return run_gemm_tc_inst<BN, EPI_RESIDUAL, OUT_F32>(st, ta, tb, p, "k_gemm_tc.residual_f32");
-            case EPI_RESIDUAL_STATS: return run_gemm_tc_inst<BN, EPI_RESIDUAL_STATS, OUT_F32>(st, ta, tb, p, "k_gemm_tc.residual_f32");
+            case EPI_RESIDUAL_STATS: return run_gemm_tc_inst<BN, EPI_RESIDUAL_STATS, OUT_F32>(st, ta, tb, p, "k_gemm_tc.residual_stats_f32");
             default: break;
         }
     }
@@ -747,7 +833,8 @@ static dl4s_status run_gemm_tc(DeviceState *st, const CUtensorMap &ta, const CUt
 
 dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_half, int64_t M, int64_t N, int64_t K,
                              int epilogue, const float *bias, const float *residual, const GemmTcOut &out,
-                             int64_t a_groups, int64_t a_group_stride, int b_split, const DropoutSpec *drop)
+                             int64_t a_groups, int64_t a_group_stride, int b_split, const DropoutSpec *drop,
+                             int64_t b_split_from_col)
 {
     DL4S_REQUIRE(gemm_tc_supported(M, N, K), "shape not supported by the tensor-core gemm");
     DL4S_REQUIRE(2 * K < (1ll << 31), "K too large");
@@ -770,6 +857,10 @@ dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_
     p.M = M; p.N = N; p.K = Kb;
     p.a_kc = (int)kc;
     p.a_groups = (int)a_groups;
+    // Columns below b_split_from_col take W_hi alone; it has to fall on a tile boundary (else every column takes both).
+    const int64_t bn = gemm_tc_wide_tiles(N) ? 256 : 128;
+    p.kblocks_hi = (int)(K / GK);
+    p.lo_from_tn = (b_split && b_split_from_col > 0 && b_split_from_col % bn == 0) ? (int)(b_split_from_col / bn) : 0;
     p.drop = drop ? *drop : DropoutSpec();
     DL4S_REQUIRE(p.drop.threshold == 0 || epi_has_residual(epilogue), "dropout is fused into the residual epilogues only");
     p.ln_stats = out.ln_stats;

@@ -43,12 +43,14 @@ struct GemmTcOut {
 int gemm_tc_stats_per_row_block(int64_t N);
 // b_split != 0: `b_half` is [2K, N], the half-rounded matrix on top of the half-rounded remainder (W_hi; W_lo); the
 // product is A W_hi + A W_lo in one accumulator, i.e. B enters with ~22 significant bits at twice the MMA work.
+// b_split_from_col > 0 (a multiple of the tile width): only the columns from there on take the remainder; the columns
+// before it are A W_hi alone at the plain product's cost.
 // A may be given as `a_groups` column blocks: element (m, g*K/a_groups + c) lies at
 // a_half[g * a_group_stride + m * K/a_groups + c] (the rank-major layout of an all-gather).
 dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_half, int64_t M, int64_t N, int64_t K,
                              int epilogue, const float *bias, const float *residual, const GemmTcOut &out,
                              int64_t a_groups = 1, int64_t a_group_stride = 0, int b_split = 0,
-                             const DropoutSpec *drop = nullptr);
+                             const DropoutSpec *drop = nullptr, int64_t b_split_from_col = 0);
 dl4s_status launch_f32_to_f16(DeviceState *st, const float *x, void *y, int64_t n);
 // hi = half(x), lo = half(x - hi): the two-half form of a weight matrix (b_split above reads [hi; lo] stacked along k).
 dl4s_status launch_f32_to_f16_hilo(DeviceState *st, const float *x, void *hi, void *lo, int64_t n);

@@ -48,6 +48,17 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// Arrivals without release semantics, for hand-offs that publish no memory of the arriving thread: a release
+// arrive waits until every earlier global store or atomic of the thread has been performed (thousands of cycles
+// after an epilogue's stores), which is what the consumer of the barrier would then wait for.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t *bar)
+{
+    asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_relaxed(uint64_t *bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.relaxed.cta.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity)
 {
     uint32_t ok;
@@ -260,6 +271,10 @@ __device__ __forceinline__ uint32_t mapa_u32(const void *p, uint32_t cta)
 __device__ __forceinline__ void mbar_arrive_remote(uint64_t *bar, uint32_t cta)
 {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(mapa_u32(bar, cta)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_remote_relaxed(uint64_t *bar, uint32_t cta)
+{
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(mapa_u32(bar, cta)) : "memory");
 }
 __device__ __forceinline__ void st_remote_u32(void *p, uint32_t cta, uint32_t v)
 {

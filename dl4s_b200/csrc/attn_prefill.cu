@@ -455,6 +455,297 @@ __global__ void __launch_bounds__(at_threads(NT), NT == 2 ? 1 : 2) k_attn_prefil
     if (warp == W_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// Persistent form of the one-tile kernel for 64-wide heads without a causal mask (the encoder's attention): at most
+// two CTAs per SM stay resident and work through the (query block, batch x head) items i, i + gridDim.x, ... .
+// With sequences of a few hundred keys an item is 2-4 key tiles, and a CTA that lives for one item spends about as
+// long on its start (barriers, tensor-memory allocation, first loads), on the wait for the first scores and on the
+// output pass as on the key tiles themselves. Here the barriers and the tensor memory are set up once; Q has two
+// buffers and the output accumulator two places in tensor memory (S [0,128) O_even [128,192) O_odd [192,256)), so
+// the producer loads the next item's Q, K and V while the current item is still being worked on, the MMA thread
+// issues the next item's first scores right behind the current item's last P V, and those MMAs run while the softmax
+// warps normalise and write out the current item's rows. Barrier phases simply continue across items.
+template <int D>
+__global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_constant__ CUtensorMap tmap_q,
+                                                                 const __grid_constant__ CUtensorMap tmap_k,
+                                                                 const __grid_constant__ CUtensorMap tmap_v, AttnTcParams p)
+{
+    static_assert(D == 64, "the persistent form is written for 64-wide heads");
+    constexpr uint32_t TILE_BYTES = AT_TILE * 128;      // 128 rows x 64 halves
+    constexpr int STAGES = 2;
+    constexpr int W_TMA = 4, W_MMA = 5;
+    constexpr uint32_t TMEM_COLS = 256;
+    constexpr uint32_t IDESC_S = idesc_f16(128, 128, 0, 0);
+    constexpr uint32_t IDESC_O = idesc_f16(128, D, 0, 1);
+    constexpr uint32_t TM_S = 0, TM_O = 128;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQ = smem;                                  // two buffers
+    uint8_t *sK = sQ + 2 * TILE_BYTES;
+    uint8_t *sV = sK + STAGES * TILE_BYTES;
+    __shared__ uint64_t q_full[2], q_empty[2], k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    __shared__ uint64_t s_full, p_ready, o_done;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total = p.nqb * p.BH;
+
+    // One item: query block qb of (batch, head) pair bh, in the same order as the one-item-per-CTA form.
+    struct Item { int bh, b, h, row0, n_t, kv_limit; bool uniform; };
+    auto decode = [&](int item) -> Item {
+        Item w;
+        const int per_group = p.nqb * AT_HEAD_GROUP;
+        const int group = item / per_group;
+        const int r = item - group * per_group;
+        const int gsize = min(AT_HEAD_GROUP, p.BH - group * AT_HEAD_GROUP);
+        const int qb = p.nqb - 1 - r / gsize;
+        w.bh = group * AT_HEAD_GROUP + r % gsize;
+        w.b = w.bh / (int)p.H;
+        w.h = w.bh % (int)p.H;
+        int len = p.lens ? p.lens[w.b] : p.Sk;
+        if (len > p.Sk) len = p.Sk;
+        w.uniform = len <= 0;                    // every key blocked: equal weights over all Sk keys
+        w.kv_limit = w.uniform ? p.Sk : len;
+        w.row0 = qb * AT_TILE;
+        w.n_t = (w.kv_limit + AT_TILE - 1) / AT_TILE;   // >= 1: Sk >= 1 and row0 < Sq by construction of the grid
+        return w;
+    };
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < 2; ++s) { mbar_init(&q_full[s], 1); mbar_init(&q_empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+            mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+        }
+        mbar_init(&s_full, 1); mbar_init(&p_ready, 128); mbar_init(&o_done, 1);
+        abort_s = 0;
+        fence_mbar_init();
+    }
+    if (warp == W_MMA) { tmem_alloc(&tmem_base_s, TMEM_COLS); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    volatile int *abort_flag = &abort_s;
+
+    if (warp >= 4) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == W_TMA) {
+            // ------------------------------------------------------------ TMA producer
+            if (elect_one()) {
+                tma_prefetch_desc(&tmap_q);
+                tma_prefetch_desc(&tmap_k);
+                tma_prefetch_desc(&tmap_v);
+                uint32_t ks = 0, kph = 0, vs = 0, vph = 0;
+                bool ok = true;
+                for (int it = 0, item = blockIdx.x; ok && item < total; ++it, item += gridDim.x) {
+                    const Item w = decode(item);
+                    const int qbuf = it & 1;
+                    // the buffer's previous user (item it-2) has issued its last Q K^T
+                    if (!(ok = mbar_wait(&q_empty[qbuf], ((it >> 1) & 1) ^ 1, abort_flag))) break;
+                    mbar_expect_tx(&q_full[qbuf], TILE_BYTES);
+                    tma_load_3d(sQ + qbuf * TILE_BYTES, &tmap_q, &q_full[qbuf], 0, w.row0, w.bh);
+                    for (int j = 0; j < w.n_t; ++j) {
+                        if (!(ok = mbar_wait(&k_empty[ks], kph ^ 1, abort_flag))) break;
+                        mbar_expect_tx(&k_full[ks], TILE_BYTES);
+                        tma_load_3d(sK + ks * TILE_BYTES, &tmap_k, &k_full[ks], 0, j * AT_TILE, w.bh);
+                        if (++ks == STAGES) { ks = 0; kph ^= 1; }
+                        if (!(ok = mbar_wait(&v_empty[vs], vph ^ 1, abort_flag))) break;
+                        mbar_expect_tx(&v_full[vs], TILE_BYTES);
+                        tma_load_3d(sV + vs * TILE_BYTES, &tmap_v, &v_full[vs], 0, j * AT_TILE, w.bh);
+                        if (++vs == STAGES) { vs = 0; vph ^= 1; }
+                    }
+                }
+            }
+        } else if (warp == W_MMA) {
+            // -------------------------------------------------------------- MMA issuer
+            if (elect_one()) {
+                uint32_t ks = 0, kph = 0, vs = 0, vph = 0, cnt = 0;   // cnt: key tiles handled so far (all items)
+                bool ok = true;
+                auto issue_qk = [&](uint32_t qbase, uint32_t kbase) {
+#pragma unroll
+                    for (int k16 = 0; k16 < D / 16; ++k16)
+                        umma_ss(tmem_base + TM_S, smem_desc_sw128(qbase + k16 * 32, 16, 1024),
+                                smem_desc_sw128(kbase + k16 * 32, 16, 1024), IDESC_S, k16 != 0);
+                    umma_commit(&s_full);
+                };
+                for (int it = 0, item = blockIdx.x; ok && item < total; ++it, item += gridDim.x) {
+                    const Item w = decode(item);
+                    const int qbuf = it & 1;
+                    const uint32_t qbase = smem_u32(sQ + qbuf * TILE_BYTES);
+                    const uint32_t o_tmem = tmem_base + TM_O + (uint32_t)(it & 1) * D;
+                    if (!(ok = mbar_wait(&q_full[qbuf], (it >> 1) & 1, abort_flag))) break;
+                    // scores of key tile 0 (behind the previous item's last P V in the tensor pipe)
+                    if (!(ok = mbar_wait(&k_full[ks], kph, abort_flag))) break;
+                    tc_fence_after();
+                    issue_qk(qbase, smem_u32(sK + ks * TILE_BYTES));
+                    umma_commit(&k_empty[ks]);
+                    if (++ks == STAGES) { ks = 0; kph ^= 1; }
+                    if (w.n_t == 1) umma_commit(&q_empty[qbuf]);
+                    for (int j = 0; j < w.n_t; ++j) {
+                        if (!(ok = mbar_wait(&v_full[vs], vph, abort_flag))) break;
+                        const uint32_t vbase = smem_u32(sV + vs * TILE_BYTES);
+                        if (!(ok = mbar_wait(&p_ready, cnt & 1, abort_flag))) break;
+                        ++cnt;
+                        tc_fence_after();
+#pragma unroll
+                        for (int k16 = 0; k16 < AT_TILE / 16; ++k16)
+                            umma_ts(o_tmem, tmem_base + TM_S + k16 * 8, smem_desc_mn_sw128(vbase + k16 * 2048, TILE_BYTES, 1024),
+                                    IDESC_O, (j | k16) != 0);
+                        umma_commit(&o_done);
+                        umma_commit(&v_empty[vs]);
+                        if (++vs == STAGES) { vs = 0; vph ^= 1; }
+                        if (j + 1 < w.n_t) {
+                            if (!(ok = mbar_wait(&k_full[ks], kph, abort_flag))) break;
+                            tc_fence_after();
+                            issue_qk(qbase, smem_u32(sK + ks * TILE_BYTES));
+                            umma_commit(&k_empty[ks]);
+                            if (++ks == STAGES) { ks = 0; kph ^= 1; }
+                            if (j + 2 == w.n_t) umma_commit(&q_empty[qbuf]);   // that was the item's last use of Q
+                        }
+                    }
+                }
+            }
+        }
+    } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
+        // ------------------------------------------------- softmax, one query row per thread
+        const int quarter = warp & 3;
+        const int r_local = quarter * 32 + lane;
+        const uint32_t tm_s = tmem_addr(tmem_base, quarter * 32, TM_S);
+        uint32_t cnt = 0;        // key tiles handled so far (all items): phase of s_full, and of o_done one behind
+        bool ok = true;
+        for (int it = 0, item = blockIdx.x; ok && item < total; ++it, item += gridDim.x) {
+            const Item w = decode(item);
+            const int row = w.row0 + r_local;
+            const uint32_t tm_o = tmem_addr(tmem_base, quarter * 32, TM_O + (uint32_t)(it & 1) * D);
+            float m_used = -INFINITY, l_sum = 0.f;
+            for (int j = 0; j < w.n_t; ++j, ++cnt) {
+                if (!(ok = mbar_wait(&s_full, cnt & 1, abort_flag))) break;
+                tc_fence_after();
+                uint32_t r[4][32];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, r[c]);
+                tmem_wait_ld();
+                const int limit = w.kv_limit - j * AT_TILE;   // columns at or beyond it are blocked in this tile
+                if (w.uniform) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[c][i] = 0u;   // all scores equal
+                }
+                if (limit < AT_TILE) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i >= limit) r[c][i] = 0xff800000u;   // -inf
+                }
+                float mc[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    mc[c] = fmaxf(__uint_as_float(r[c][0]), __uint_as_float(r[c][1]));
+#pragma unroll
+                    for (int i = 2; i < 32; i += 2) mc[c] = max3(mc[c], __uint_as_float(r[c][i]), __uint_as_float(r[c][i + 1]));
+                }
+                const float mx = fmaxf(fmaxf(mc[0], mc[1]), fmaxf(mc[2], mc[3]));
+                // Lazy rescale, as in the one-item form: only when the row max has grown by more than 2^8.
+                float alpha = 1.0f;
+                const bool need = mx > m_used + 8.0f;
+                if (need) {
+                    alpha = fast_exp2(m_used - mx);
+                    m_used = mx;
+                    l_sum *= alpha;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, need)) {
+                    if (!(ok = mbar_wait(&o_done, (cnt - 1) & 1, abort_flag))) break;
+                    tc_fence_after();
+#pragma unroll 1
+                    for (int c = 0; c < D / 32; ++c) {
+                        uint32_t o[32];
+                        tmem_ld32(tm_o + c * 32, o);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(tm_o + c * 32, o);
+                    }
+                }
+                const uint64_t negm2 = pack2(-m_used, -m_used);
+                uint64_t acc0 = pack2(0.f, 0.f), acc1 = acc0;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        uint64_t x2 = add2(pack2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), negm2);
+                        float p0, p1, x0, x1;
+                        unpack2(x2, x0, x1);
+                        p0 = fast_exp2(x0);
+                        p1 = fast_exp2(x1);
+                        if (i & 1) acc1 = add2(acc1, pack2(p0, p1));
+                        else acc0 = add2(acc0, pack2(p0, p1));
+                        pk[i] = pack_half2(p0, p1);
+                    }
+                    tmem_st16(tm_s + c * 16, pk);
+                }
+                {
+                    float a, b2;
+                    unpack2(add2(acc0, acc1), a, b2);
+                    l_sum += a + b2;
+                }
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(&p_ready);
+            }
+            if (!ok) break;
+            // O / l for this item; the next item's first scores are being computed meanwhile.
+            if (!(ok = mbar_wait(&o_done, (cnt - 1) & 1, abort_flag))) break;
+            tc_fence_after();
+            const float inv_l = 1.0f / l_sum;
+            if (p.lse && row < p.Sq) p.lse[(int64_t)w.bh * p.Sq + row] = m_used + log2f(l_sum);
+            const int64_t ooff = (int64_t)w.b * p.os.b + (int64_t)w.h * p.os.h + (int64_t)row * p.os.s;
+            float *orow = reinterpret_cast<float *>(p.o) + ooff;
+            __half *hrow = reinterpret_cast<__half *>(p.o) + ooff;
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t o[32];
+                tmem_ld32(tm_o + c * 32, o);
+                tmem_wait_ld();
+                if (row < p.Sq) {
+                    if (p.o_half) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 8) {
+                            uint4 pk;
+                            pk.x = pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                            pk.y = pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                            pk.z = pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                            pk.w = pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                            *reinterpret_cast<uint4 *>(hrow + c * 32 + i) = pk;
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4)
+                            *reinterpret_cast<float4 *>(orow + c * 32 + i) =
+                                make_float4(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l,
+                                            __uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                    }
+                }
+            }
+            // The accumulator this item used is written again two items from now, behind the next item's softmax.
+            tc_fence_before();
+        }
+    }
+
+    // Common exit, also reached after a wait that gave up.
+    tc_fence_before();
+    __syncthreads();
+    if (threadIdx.x == 0 && abort_s) atomicOr(p.status, kStatusAttnTimeout);
+    if (warp == W_MMA) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 bool attn_prefill_tc_supported(int64_t Sq, int64_t Sk, int64_t dk, int64_t dv)
 {
     return dk == dv && (dk == 64 || dk == 128) && Sq >= 1 && Sk >= 1 && Sq < (1 << 30) && Sk < (1 << 30);
@@ -546,6 +837,21 @@ dl4s_status launch_attn_prefill_tc_h(DeviceState *st, const void *qh, const void
     // output pass behind. One query tile per CTA and two CTAs per SM: each CTA's serial parts run under the
     // other's softmax.
     p.nqb = (int)ceil_div(Sq, AT_TILE);
+    if (!mask.causal) {
+        // every item of a (batch, head) pair costs the same: resident CTAs with a fixed round-robin share
+        constexpr size_t smem = (size_t)6 * AT_TILE * 128 + 1024;
+        static bool attr_set[kMaxDevices] = {false};
+        if (!attr_set[st->ordinal]) {
+            DL4S_CUDA_TRY(cudaFuncSetAttribute(k_attn_prefill_tc_loop<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            attr_set[st->ordinal] = true;
+        }
+        DL4S_REQUIRE((int64_t)p.nqb * BH < (1ll << 31), "too many query blocks for one grid");
+        p.BH = (int)BH;
+        const int64_t items = (int64_t)p.nqb * BH, resident = 2 * (int64_t)st->sm_count;
+        DL4S_CUDA_TRY(launch_pdl(st, k_attn_prefill_tc_loop<64>, dim3((unsigned)(items < resident ? items : resident)), dim3(256), smem, 1,
+                                 tq, tk, tv, p));
+        return after_launch(st, "k_attn_prefill_tc_loop");
+    }
     return run_attn_tc<64, 1>(st, tq, tk, tv, p, BH);
 }
 

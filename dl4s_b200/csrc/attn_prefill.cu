@@ -459,11 +459,13 @@ __global__ void __launch_bounds__(at_threads(NT), NT == 2 ? 1 : 2) k_attn_prefil
 // two CTAs per SM stay resident and work through the (query block, batch x head) items i, i + gridDim.x, ... .
 // With sequences of a few hundred keys an item is 2-4 key tiles, and a CTA that lives for one item spends about as
 // long on its start (barriers, tensor-memory allocation, first loads), on the wait for the first scores and on the
-// output pass as on the key tiles themselves. Here the barriers and the tensor memory are set up once; Q has two
-// buffers and the output accumulator two places in tensor memory (S [0,128) O_even [128,192) O_odd [192,256)), so
-// the producer loads the next item's Q, K and V while the current item is still being worked on, the MMA thread
-// issues the next item's first scores right behind the current item's last P V, and those MMAs run while the softmax
-// warps normalise and write out the current item's rows. Barrier phases simply continue across items.
+// output pass as on the key tiles themselves. Here the barriers and the tensor memory are set up once, Q has two
+// buffers, and the producer loads the next item's Q, K and V while the current item is still being worked on.
+// The probabilities have their own tensor-memory columns (S [0,128) P [128,192) O [192,256)) instead of lying over
+// the scores, so the MMA thread issues the scores of key tile g+1 as soon as the softmax warps have READ tile g
+// (s_free), in front of P_g V_g: the softmax warps find the next scores ready when they finish a tile, across item
+// boundaries as well, and a key tile costs one softmax pass (bound by the exp2 unit) instead of softmax + MMAs +
+// hand-offs in series. Barrier phases continue across items (g counts this CTA's key tiles).
 template <int D>
 __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_constant__ CUtensorMap tmap_q,
                                                                  const __grid_constant__ CUtensorMap tmap_k,
@@ -476,7 +478,7 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
     constexpr uint32_t TMEM_COLS = 256;
     constexpr uint32_t IDESC_S = idesc_f16(128, 128, 0, 0);
     constexpr uint32_t IDESC_O = idesc_f16(128, D, 0, 1);
-    constexpr uint32_t TM_S = 0, TM_O = 128;
+    constexpr uint32_t TM_S = 0, TM_P = 128, TM_O = 192;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -484,7 +486,7 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
     uint8_t *sK = sQ + 2 * TILE_BYTES;
     uint8_t *sV = sK + STAGES * TILE_BYTES;
     __shared__ uint64_t q_full[2], q_empty[2], k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
-    __shared__ uint64_t s_full, p_ready, o_done;
+    __shared__ uint64_t s_full, s_free, p_ready, o_done;
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
@@ -520,7 +522,7 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
             mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
             mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
         }
-        mbar_init(&s_full, 1); mbar_init(&p_ready, 128); mbar_init(&o_done, 1);
+        mbar_init(&s_full, 1); mbar_init(&s_free, 128); mbar_init(&p_ready, 128); mbar_init(&o_done, 1);
         abort_s = 0;
         fence_mbar_init();
     }
@@ -563,50 +565,58 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
         } else if (warp == W_MMA) {
             // -------------------------------------------------------------- MMA issuer
             if (elect_one()) {
-                uint32_t ks = 0, kph = 0, vs = 0, vph = 0, cnt = 0;   // cnt: key tiles handled so far (all items)
+                uint32_t ks = 0, kph = 0, vs = 0, vph = 0;
                 bool ok = true;
-                auto issue_qk = [&](uint32_t qbase, uint32_t kbase) {
+                // Two walks over this CTA's key tiles: `sc` is the tile whose scores are issued next (one ahead),
+                // `pv` the tile whose P V is issued next.
+                struct Walk { int it, item, j, n_t; };
+                Walk sc{0, (int)blockIdx.x, 0, 0}, pv{0, (int)blockIdx.x, 0, 0};
+                if (sc.item < total) sc.n_t = pv.n_t = decode(sc.item).n_t;
+                auto advance = [&](Walk &w) {
+                    if (++w.j == w.n_t) {
+                        w.j = 0;
+                        ++w.it;
+                        w.item += (int)gridDim.x;
+                        w.n_t = w.item < total ? decode(w.item).n_t : 0;
+                    }
+                };
+                // Scores of tile `sc` (its K tile is next in the ring); false after a wait that gave up.
+                auto issue_scores = [&]() -> bool {
+                    const int qbuf = sc.it & 1;
+                    if (sc.j == 0 && !mbar_wait(&q_full[qbuf], (sc.it >> 1) & 1, abort_flag)) return false;
+                    if (!mbar_wait(&k_full[ks], kph, abort_flag)) return false;
+                    tc_fence_after();
+                    const uint32_t qbase = smem_u32(sQ + qbuf * TILE_BYTES), kbase = smem_u32(sK + ks * TILE_BYTES);
 #pragma unroll
                     for (int k16 = 0; k16 < D / 16; ++k16)
                         umma_ss(tmem_base + TM_S, smem_desc_sw128(qbase + k16 * 32, 16, 1024),
                                 smem_desc_sw128(kbase + k16 * 32, 16, 1024), IDESC_S, k16 != 0);
                     umma_commit(&s_full);
-                };
-                for (int it = 0, item = blockIdx.x; ok && item < total; ++it, item += gridDim.x) {
-                    const Item w = decode(item);
-                    const int qbuf = it & 1;
-                    const uint32_t qbase = smem_u32(sQ + qbuf * TILE_BYTES);
-                    const uint32_t o_tmem = tmem_base + TM_O + (uint32_t)(it & 1) * D;
-                    if (!(ok = mbar_wait(&q_full[qbuf], (it >> 1) & 1, abort_flag))) break;
-                    // scores of key tile 0 (behind the previous item's last P V in the tensor pipe)
-                    if (!(ok = mbar_wait(&k_full[ks], kph, abort_flag))) break;
-                    tc_fence_after();
-                    issue_qk(qbase, smem_u32(sK + ks * TILE_BYTES));
                     umma_commit(&k_empty[ks]);
                     if (++ks == STAGES) { ks = 0; kph ^= 1; }
-                    if (w.n_t == 1) umma_commit(&q_empty[qbuf]);
-                    for (int j = 0; j < w.n_t; ++j) {
-                        if (!(ok = mbar_wait(&v_full[vs], vph, abort_flag))) break;
-                        const uint32_t vbase = smem_u32(sV + vs * TILE_BYTES);
-                        if (!(ok = mbar_wait(&p_ready, cnt & 1, abort_flag))) break;
-                        ++cnt;
-                        tc_fence_after();
-#pragma unroll
-                        for (int k16 = 0; k16 < AT_TILE / 16; ++k16)
-                            umma_ts(o_tmem, tmem_base + TM_S + k16 * 8, smem_desc_mn_sw128(vbase + k16 * 2048, TILE_BYTES, 1024),
-                                    IDESC_O, (j | k16) != 0);
-                        umma_commit(&o_done);
-                        umma_commit(&v_empty[vs]);
-                        if (++vs == STAGES) { vs = 0; vph ^= 1; }
-                        if (j + 1 < w.n_t) {
-                            if (!(ok = mbar_wait(&k_full[ks], kph, abort_flag))) break;
-                            tc_fence_after();
-                            issue_qk(qbase, smem_u32(sK + ks * TILE_BYTES));
-                            umma_commit(&k_empty[ks]);
-                            if (++ks == STAGES) { ks = 0; kph ^= 1; }
-                            if (j + 2 == w.n_t) umma_commit(&q_empty[qbuf]);   // that was the item's last use of Q
-                        }
+                    if (sc.j == sc.n_t - 1) umma_commit(&q_empty[qbuf]);   // the item's last use of Q
+                    advance(sc);
+                    return true;
+                };
+                if (sc.item < total) ok = issue_scores();
+                for (uint32_t g = 0; ok && pv.item < total; ++g) {
+                    // the next tile's scores go in front of this tile's P V, once the softmax warps have read S_g
+                    if (sc.item < total) {
+                        if (!(ok = mbar_wait(&s_free, g & 1, abort_flag))) break;
+                        if (!(ok = issue_scores())) break;
                     }
+                    if (!(ok = mbar_wait(&v_full[vs], vph, abort_flag))) break;
+                    const uint32_t vbase = smem_u32(sV + vs * TILE_BYTES);
+                    if (!(ok = mbar_wait(&p_ready, g & 1, abort_flag))) break;
+                    tc_fence_after();
+#pragma unroll
+                    for (int k16 = 0; k16 < AT_TILE / 16; ++k16)
+                        umma_ts(tmem_base + TM_O, tmem_base + TM_P + k16 * 8, smem_desc_mn_sw128(vbase + k16 * 2048, TILE_BYTES, 1024),
+                                IDESC_O, (pv.j | k16) != 0);
+                    umma_commit(&o_done);
+                    umma_commit(&v_empty[vs]);
+                    if (++vs == STAGES) { vs = 0; vph ^= 1; }
+                    advance(pv);
                 }
             }
         }
@@ -616,20 +626,24 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
         const int quarter = warp & 3;
         const int r_local = quarter * 32 + lane;
         const uint32_t tm_s = tmem_addr(tmem_base, quarter * 32, TM_S);
-        uint32_t cnt = 0;        // key tiles handled so far (all items): phase of s_full, and of o_done one behind
+        const uint32_t tm_p = tmem_addr(tmem_base, quarter * 32, TM_P);
+        const uint32_t tm_o = tmem_addr(tmem_base, quarter * 32, TM_O);
+        uint32_t g = 0;          // this CTA's key tiles so far: phase of s_full / s_free / p_ready, and of o_done one behind
         bool ok = true;
         for (int it = 0, item = blockIdx.x; ok && item < total; ++it, item += gridDim.x) {
             const Item w = decode(item);
             const int row = w.row0 + r_local;
-            const uint32_t tm_o = tmem_addr(tmem_base, quarter * 32, TM_O + (uint32_t)(it & 1) * D);
             float m_used = -INFINITY, l_sum = 0.f;
-            for (int j = 0; j < w.n_t; ++j, ++cnt) {
-                if (!(ok = mbar_wait(&s_full, cnt & 1, abort_flag))) break;
+            for (int j = 0; j < w.n_t; ++j, ++g) {
+                if (!(ok = mbar_wait(&s_full, g & 1, abort_flag))) break;
                 tc_fence_after();
                 uint32_t r[4][32];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(tm_s + c * 32, r[c]);
                 tmem_wait_ld();
+                // the scores are in registers: the next tile's may be written
+                tc_fence_before();
+                mbar_arrive(&s_free);
                 const int limit = w.kv_limit - j * AT_TILE;   // columns at or beyond it are blocked in this tile
                 if (w.uniform) {
 #pragma unroll
@@ -660,24 +674,11 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
                     m_used = mx;
                     l_sum *= alpha;
                 }
-                if (j > 0 && __any_sync(0xffffffffu, need)) {
-                    if (!(ok = mbar_wait(&o_done, (cnt - 1) & 1, abort_flag))) break;
-                    tc_fence_after();
-#pragma unroll 1
-                    for (int c = 0; c < D / 32; ++c) {
-                        uint32_t o[32];
-                        tmem_ld32(tm_o + c * 32, o);
-                        tmem_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(tm_o + c * 32, o);
-                    }
-                }
                 const uint64_t negm2 = pack2(-m_used, -m_used);
                 uint64_t acc0 = pack2(0.f, 0.f), acc1 = acc0;
+                uint32_t pk[4][16];
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         uint64_t x2 = add2(pack2(__uint_as_float(r[c][2 * i]), __uint_as_float(r[c][2 * i + 1])), negm2);
@@ -687,22 +688,41 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
                         p1 = fast_exp2(x1);
                         if (i & 1) acc1 = add2(acc1, pack2(p0, p1));
                         else acc0 = add2(acc0, pack2(p0, p1));
-                        pk[i] = pack_half2(p0, p1);
+                        pk[c][i] = pack_half2(p0, p1);
                     }
-                    tmem_st16(tm_s + c * 16, pk);
                 }
                 {
                     float a, b2;
                     unpack2(add2(acc0, acc1), a, b2);
                     l_sum += a + b2;
                 }
+                // P_{g-1} V_{g-1} must have finished with the P columns (and with O, if it is rescaled) before they
+                // are written again. Within an item that is o_done of the tile before; across items the previous
+                // item's output pass has already waited for it.
+                if (j > 0) {
+                    if (!(ok = mbar_wait(&o_done, (g - 1) & 1, abort_flag))) break;
+                    tc_fence_after();
+                    if (__any_sync(0xffffffffu, need)) {
+#pragma unroll 1
+                        for (int c = 0; c < D / 32; ++c) {
+                            uint32_t o[32];
+                            tmem_ld32(tm_o + c * 32, o);
+                            tmem_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(tm_o + c * 32, o);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_st16(tm_p + c * 16, pk[c]);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(&p_ready);
             }
             if (!ok) break;
-            // O / l for this item; the next item's first scores are being computed meanwhile.
-            if (!(ok = mbar_wait(&o_done, (cnt - 1) & 1, abort_flag))) break;
+            // O / l for this item; the next item's first scores are already in tensor memory or on their way.
+            if (!(ok = mbar_wait(&o_done, (g - 1) & 1, abort_flag))) break;
             tc_fence_after();
             const float inv_l = 1.0f / l_sum;
             if (p.lse && row < p.Sq) p.lse[(int64_t)w.bh * p.Sq + row] = m_used + log2f(l_sum);
@@ -718,12 +738,12 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
                     if (p.o_half) {
 #pragma unroll
                         for (int i = 0; i < 32; i += 8) {
-                            uint4 pk;
-                            pk.x = pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
-                            pk.y = pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
-                            pk.z = pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
-                            pk.w = pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
-                            *reinterpret_cast<uint4 *>(hrow + c * 32 + i) = pk;
+                            uint4 pk4;
+                            pk4.x = pack_half2(__uint_as_float(o[i]) * inv_l, __uint_as_float(o[i + 1]) * inv_l);
+                            pk4.y = pack_half2(__uint_as_float(o[i + 2]) * inv_l, __uint_as_float(o[i + 3]) * inv_l);
+                            pk4.z = pack_half2(__uint_as_float(o[i + 4]) * inv_l, __uint_as_float(o[i + 5]) * inv_l);
+                            pk4.w = pack_half2(__uint_as_float(o[i + 6]) * inv_l, __uint_as_float(o[i + 7]) * inv_l);
+                            *reinterpret_cast<uint4 *>(hrow + c * 32 + i) = pk4;
                         }
                     } else {
 #pragma unroll
@@ -734,7 +754,7 @@ __global__ void __launch_bounds__(256, 2) k_attn_prefill_tc_loop(const __grid_co
                     }
                 }
             }
-            // The accumulator this item used is written again two items from now, behind the next item's softmax.
+            // O is written again by the next item's first P V, which waits for this thread's next p_ready.
             tc_fence_before();
         }
     }

@@ -550,12 +550,18 @@ def run_encoder(args, gpu, peaks):
             alg = L * 2 * (3 * B * S * D * 4)      # two LayerNorms per layer, read twice + write once
             unit, peak, bound = "GB/s", peaks["hbm_gbs"], "hbm"
             ach = alg / (ms_dom * 1e-3) / 1e9
-        # DRAM bytes of the GEMM launches of one step come from an ncu pass over this same command (single-rounded
-        # weights, this exact configuration); other kernels and modes were not captured.
-        tr, stale = ncu_traffic("k_gemm_tc.encoder_step")
-        use = tr and "gemm" in dom and (B, S, D, F, L) == (32, 512, 512, 2048, 6) and args.precision == "f16"
+        # DRAM bytes of the GEMM launches of one step come from an ncu pass over this same command (this exact
+        # configuration, one capture per precision); other kernels were not captured.
+        tr, stale = ncu_traffic("k_gemm_tc.encoder_step." + args.precision)
+        use = tr and "gemm" in dom and (B, S, D, F, L) == (32, 512, 512, 2048, 6)
         traffic = tr["bytes"] if use else None
+        # Two-half weights: the products against Wv, Wo, W1 and W2 run twice (W_hi and W_lo), the q and k columns once.
+        executed = 1.0
+        if "gemm" in dom and args.precision == "f16_split":
+            executed = (L * (2 * B * S * D * (2 * H * cfg["dk"]) + 2 * 2 * B * S * D * (H * cfg["dv"])
+                             + 2 * 2 * B * S * H * cfg["dv"] * D + 2 * 4 * B * S * D * F)) / gemm_flops
         roof = {"bound": bound, "kernel": dom, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak, "traffic": traffic,
+                "mma_flops_executed_per_algorithmic_flop": executed, "frac_of_executed_flops": ach * executed / peak,
                 "traffic_source": {"capture": tr["summary"], "kernel_source_changed_since_capture": stale} if use else None,
                 "launches_per_step": prof[dom]["launches"], "ms_per_step": ms_dom,
                 "peak_source": peaks["source"], "share_of_step": ms_dom / max(sum(v["total_ms"] for v in prof.values()), 1e-9)}
@@ -584,6 +590,25 @@ def run_encoder(args, gpu, peaks):
         "clocks": clocks, "roofline": roof,
         "kernel_profile_ms_per_step": {k: round(v["total_ms"], 4) for k, v in prof_detail.items()},
     }
+    if args.precision == "f16_split":
+        # The same step with every operand rounded to half once: what the two-half weights cost, and what they buy
+        # (errors of both against the CPU run are in cpu_baseline.agreement_with_gpu and here).
+        enc1 = TransformerEncoder(L, H, cfg["dk"], cfg["dv"], D, F, layers=cfg["layers"], precision=PREC_F16)
+        out1 = cuda.CUDA.Memory.allocateBuffer((B, S, D))
+        enc1(x, mask, out=out1)
+        g1 = None
+        if not args.no_graph:
+            with cuda.Graph() as g1:
+                enc1(x, mask, out=out1)
+        ms1 = gpu.timed_steps((lambda: g1.launch()) if g1 is not None else (lambda: enc1(x, mask, out=out1)), args.steps, args.warmup)
+        line["single_rounded_weights"] = {
+            "precision": "f16", "value": tokens / (ms1 * 1e-3), "unit": "tokens/s", "ms_per_step": ms1 / args.steps,
+            "note": "every operand rounded to half once: faster, but 2.8e-3 max-abs on this 6-layer stack, outside the stated "
+                    "2e-3; not the headline for that reason"}
+        first_rows_f16 = out1.numpy()[:4] if (gpu.rank == 0 and gpu.world == 1) else None
+        del enc1, g1
+    else:
+        first_rows_f16 = None
     if not args.no_head_sharded:
         # the layer that spans GPUs (heads over ranks, one all-gather per batch chunk), at every N including 1
         first_rows = out.numpy()[:4] if (gpu.rank == 0 and gpu.world == 1) else None
@@ -598,6 +623,10 @@ def run_encoder(args, gpu, peaks):
             "max_abs": float(np.abs(err).max()), "rel_l2": float(np.linalg.norm(err) / np.linalg.norm(blas_out)),
             "sample": "the 4 sequences of the BLAS run, GPU output of the timed configuration against the CPU output",
             "stated_tolerance": "max-abs 2e-3, relative L2 1e-3 (tensor-core paths); 1e-5 (fp32)"}
+        if first_rows_f16 is not None:
+            e1 = first_rows_f16.astype(np.float64) - blas_out
+            line["single_rounded_weights"]["agreement_with_gpu"] = {
+                "max_abs": float(np.abs(e1).max()), "rel_l2": float(np.linalg.norm(e1) / np.linalg.norm(blas_out))}
         line["cpu_baseline"]["blas_value"] = blas_tps
         line["cpu_baseline"]["blas_cores"] = os.cpu_count()
         line["cpu_baseline"]["blas_sample"] = f"4 of 32 sequences x 6 layers in {blas_dt:.2f} s, multi-threaded BLAS sgemm"
@@ -623,14 +652,16 @@ def head_sharded_bench(args, gpu, peaks, shape=None, steps=None, warmup=3):
     chunk precedes Wo (issued by the library, dl4s_cuda_mha_forward_sharded), the second half runs per batch slice.
     Total work is fixed: strong scaling. Returns the measurements as a dict (every rank calls this; collectives)."""
     import torch
-    from dl4s_b200 import sharded
+    from dl4s_b200 import PREC_F16, PREC_FP32, sharded
     from dl4s_b200.cuda import ShapedBuffer
     from dl4s_b200.layers import xavier_uniform
     cuda = gpu.cuda
     B, S, D, H = shape or (256, 2048, 4096, 32)
     steps = steps or args.steps
     dk = D // H
-    prec = precision_of(args)
+    # One layer: operands rounded to half once stay inside the stated tolerance (the two-half weights are for deep stacks).
+    hs_precision = "fp32" if args.precision == "fp32" else "f16"
+    prec = {"fp32": PREC_FP32, "f16": PREC_F16}[hs_precision]
     rw = np.random.default_rng(0)
     weights = {n: xavier_uniform(rw, D, D) for n in ("qDense", "kDense", "vDense", "fc")}
     # X ~ N(0,1): 8.6 GB at full size, replicated on every rank; drawn on the device from a fixed seed
@@ -673,7 +704,7 @@ def head_sharded_bench(args, gpu, peaks, shape=None, steps=None, warmup=3):
     if gpu.dist is not None:
         gpu.dist.all_reduce(check)
     ms = total_ms / steps
-    esz = 4 if args.precision == "fp32" else 2
+    esz = 4 if hs_precision == "fp32" else 2
     sent = B * S * (D // gpu.world) * esz
     res = {"workload": "head_sharded_decoder_self_attention", "batch": B, "seq_len": S, "d_model": D, "heads": H, "mask": "causal",
            "n_gpus": gpu.world, "steps": steps, "warmup": warmup, "scaling": "strong", "ms_per_step": ms,
@@ -686,7 +717,7 @@ def head_sharded_bench(args, gpu, peaks, shape=None, steps=None, warmup=3):
                           "element": "f16" if esz == 2 else "f32", "nccl_version": sharded.comm_info()[2],
                           "gather_ms_per_step": gather_ms, "exposed_ms_per_step": exposed_ms,
                           "hidden_ms_per_step": max(gather_ms - exposed_ms, 0.0)},
-           "gpu_launches": launches, "clocks": clocks, "precision": args.precision,
+           "gpu_launches": launches, "clocks": clocks, "precision": hs_precision,
            "kernel_profile_ms_per_step": {k: round(v["total_ms"], 3) for k, v in prof.items()}, "sample_output": first,
            "output_abs_sum": float(check.item()), "l2": "inputs (8.6 GB) exceed L2; no flush"}
     del layer, out_t, xt
@@ -700,7 +731,7 @@ def run_decoder_mha(args, gpu, peaks):
     r = head_sharded_bench(args, gpu, peaks, shape=shape, warmup=args.warmup)
     return {"metric": "decoder_self_attention_tokens_per_s", "value": r["tokens_per_s"], "unit": "tokens/s",
             "n_gpus": gpu.world, "steps": r["steps"], "warmup": r["warmup"], "ms_per_step": r["ms_per_step"],
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE_NOTE[args.precision],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": DTYPE_NOTE[r["precision"]],
             "data": "synthetic",
             "config": {"workload": r["workload"], "batch": r["batch"], "seq_len": r["seq_len"], "d_model": r["d_model"],
                        "heads": r["heads"], "mask": "causal",
@@ -972,9 +1003,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="encoder", choices=["encoder", "prefill", "decode", "decoder_mha", "gemm", "mha", "decode_step", "head", "backward"])
-    ap.add_argument("--precision", default="f16", choices=["f16", "f16_split", "fp32"],
-                    help="f16: half operands rounded once; f16_split: weights as two halves (meets max-abs 2e-3 on the 6-layer "
-                         "encoder); fp32: FFMA check kernels")
+    ap.add_argument("--precision", default="f16_split", choices=["f16", "f16_split", "fp32"],
+                    help="f16_split (default): half operands, the weights that feed the residual stream as two halves; the "
+                         "mode that meets max-abs 2e-3 / relative L2 1e-3 on the 6-layer encoder. f16: every operand rounded "
+                         "to half once (faster, 2.8e-3 max-abs on that encoder). fp32: FFMA check kernels")
     ap.add_argument("--no-attention", action="store_true", help="skip the attention-only sections of the default line")
     ap.add_argument("--no-head-sharded", action="store_true", help="skip the head-sharded layer section of the default line")
     ap.add_argument("--no-graph", action="store_true", help="encoder workload: launch the kernels eagerly instead of replaying "

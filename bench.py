@@ -922,8 +922,10 @@ def run_backward(args, gpu, peaks):
         mask, pairs = cuda.makeEncoderMasks(lens), H * S * int(lens.sum())
     temperature = float(np.sqrt(np.float32(d)))
 
+    grads = tuple(cuda.CUDA.Memory.allocateBuffer((B, H, S, d)) for _ in range(3))
+
     def call():
-        scaledDotProductAttentionBackward(q, k, v, g, mask, temperature, PREC_F16)
+        scaledDotProductAttentionBackward(q, k, v, g, mask, temperature, PREC_F16, out=grads)
 
     flops = 10 * d * pairs
     ms_kernel, _ = kernel_time(gpu, call, "k_attn_bwd_tc", max(args.steps, 3))

@@ -101,14 +101,15 @@ class ScaledDotProductAttention:
 
 
 def scaledDotProductAttentionBackward(q: ShapedBuffer, k: ShapedBuffer, v: ShapedBuffer, dout: ShapedBuffer, mask=None,
-                                      temperature: Optional[float] = None, precision: int = _lib.PREC_FP32):
+                                      temperature: Optional[float] = None, precision: int = _lib.PREC_FP32, out=None):
     """Gradients of ScaledDotProductAttention with respect to q, k and v for the upstream gradient dout: what the
-    backward closures of DL4S's primitives produce (Matrix.swift:139-173, Unary.swift:190-194), in one call."""
+    backward closures of DL4S's primitives produce (Matrix.swift:139-173, Unary.swift:190-194), in one call.
+    `out` = (dq, dk, dv) buffers to write into (allocated here when absent)."""
     B, H, Sq, dk = q.shape
     Sk, dv = v.shape[2], v.shape[3]
     t = float(np.sqrt(np.float32(dk))) if temperature is None else float(temperature)
     lp, causal, mp, ms, _keep = _mask_args(mask)
-    dq, dkk, dvv = (CUDA.Memory.allocateBuffer(t_.shape) for t_ in (q, k, v))
+    dq, dkk, dvv = out if out is not None else (CUDA.Memory.allocateBuffer(t_.shape) for t_ in (q, k, v))
     call("dl4s_cuda_sdpa_backward", c_vp(q.ptr), c_vp(k.ptr), c_vp(v.ptr), c_vp(dout.ptr), B, H, Sq, Sk, dk, dv, c_f32(t), lp,
          causal, mp, ms, c_vp(dq.ptr), c_vp(dkk.ptr), c_vp(dvv.ptr), precision)
     return dq, dkk, dvv

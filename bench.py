@@ -747,7 +747,7 @@ def run_mha_small(args, gpu, peaks):
     """MultiHeadAttention forward, batch 8, seq 128, d_model 512, 8 heads, no mask: the one configuration the
     reference's CPU engine runs in full. 2.4 GFLOP: latency-bound on a B200, reported without a roofline claim.
     Both arithmetic paths are timed and compared with the CPU engine's output on the same arrays."""
-    from dl4s_b200 import PREC_F16, PREC_FP32, workloads
+    from dl4s_b200 import PREC_F16, PREC_F16_SPLIT, PREC_FP32, workloads
     from dl4s_b200.layers import MultiHeadAttention
     from oracle import oracle as O
     from oracle import oracle_np as ON
@@ -767,7 +767,7 @@ def run_mha_small(args, gpu, peaks):
     cpu_blas_s = (time.perf_counter() - t0) / 10
     tx = cuda.tensor(x)
     paths = {}
-    for name, prec in (("fp32", PREC_FP32), ("f16", PREC_F16)):
+    for name, prec in (("fp32", PREC_FP32), ("f16", PREC_F16), ("f16_split", PREC_F16_SPLIT)):
         layer = MultiHeadAttention(c["heads"], D, c["dk"], c["dv"], weights=w, precision=prec)
         out = cuda.CUDA.Memory.allocateBuffer((B, S, D))
         got = layer(tx, tx, tx, out=out).numpy()
@@ -782,7 +782,7 @@ def run_mha_small(args, gpu, peaks):
                        "tokens_per_s_graph_replay": B * S / (ms_graph * 1e-3), "replay_equals_eager": replay_equal,
                        "max_abs_err": float(np.abs(err).max()),
                        "rel_l2_err": float(np.linalg.norm(err) / np.linalg.norm(want)), "launches": gpu.last_timed_launches // args.steps}
-    main_path = paths["f16" if args.precision == "f16" else "fp32"]
+    main_path = paths[args.precision]
     return {"metric": "mha_tokens_per_s", "value": main_path["tokens_per_s"], "unit": "tokens/s", "n_gpus": gpu.world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": main_path["ms"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": args.precision, "data": "synthetic",

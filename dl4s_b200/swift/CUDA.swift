@@ -200,7 +200,13 @@ public struct CUDAEngine: EngineType {
         check(dl4s_cuda_stack(ptrs, shapes, Int32(buffers.count), Int32(buffers[0].dim), Int32(axis), result.values.memory.floats()))
     }
 
-    // Every remaining EngineType requirement (diagonals, min, scatter/gather, reverse, unstack,
+    public static func unstack<N>(stacked: ShapedBuffer<N, CUDA>, result: [ShapedBuffer<N, CUDA>], axis: Int) {
+        let ptrs: [UnsafeMutablePointer<Float>?] = result.map { $0.values.memory.floats() }
+        let shapes = result.flatMap { $0.shape.map(Int64.init) }
+        check(dl4s_cuda_unstack(stacked.values.memory.floats(), ptrs, shapes, Int32(result.count), Int32(result[0].dim), Int32(axis)))
+    }
+
+    // Every remaining EngineType requirement (diagonals, min, scatter/gather, reverse,
     // img2col, subscript ops, tan/sinh/cosh, arange ...) is outside the attention path:
     //     fatalError("\(#function) is not available on the CUDA device")
     // one line each, omitted here for brevity of the glue.
@@ -228,11 +234,42 @@ public extension CUDAEngine {
                                          result.values.memory.floats(), CUDA.precision))
         }
     }
-    // multiHeadAttentionForward -> dl4s_cuda_mha_forward, layerNorm -> dl4s_cuda_layernorm,
-    // feedForward -> dl4s_cuda_ffn_forward, encoderForward -> dl4s_cuda_encoder_forward,
-    // prepareInputs -> dl4s_cuda_embed_positional, the output head of Transformer.callAsFunction ->
-    // dl4s_cuda_output_head, one token of greedy decoding per decoder self-attention layer ->
-    // dl4s_cuda_mha_decode_step (with a key/value cache the Swift side owns): same pattern.
+    /// Gradients of the call above for the upstream gradient `dOut` (the backpropagate closures of the fused
+    /// attention tensor): dq, dk, dv in one call, probabilities recomputed.
+    static func scaledDotProductAttentionBackward(q: ShapedBuffer<Float, CUDA>, k: ShapedBuffer<Float, CUDA>, v: ShapedBuffer<Float, CUDA>,
+                                                  dOut: ShapedBuffer<Float, CUDA>, temperature: Float,
+                                                  keyLengths: Buffer<Int32, CUDA>?, causal: Bool,
+                                                  dq: ShapedBuffer<Float, CUDA>, dk: ShapedBuffer<Float, CUDA>, dv: ShapedBuffer<Float, CUDA>) {
+        let (B, H, Sq, dkk) = (q.shape[0], q.shape[1], q.shape[2], q.shape[3]), Sk = k.shape[2], dvv = v.shape[3]
+        check(dl4s_cuda_sdpa_backward(q.values.memory.floats(), k.values.memory.floats(), v.values.memory.floats(),
+                                      dOut.values.memory.floats(), Int64(B), Int64(H), Int64(Sq), Int64(Sk), Int64(dkk), Int64(dvv),
+                                      temperature, keyLengths?.memory.pointer?.assumingMemoryBound(to: Int32.self), causal ? 1 : 0,
+                                      nil, nil, dq.values.memory.floats(), dk.values.memory.floats(), dv.values.memory.floats(),
+                                      CUDA.precision))
+    }
+    // multiHeadAttentionForward -> dl4s_cuda_mha_forward, layerNorm -> dl4s_cuda_layernorm (backward:
+    // dl4s_cuda_layernorm_backward), feedForward -> dl4s_cuda_ffn_forward, encoderForward -> dl4s_cuda_encoder_forward
+    // (or dl4s_cuda_encoder_prepare once + dl4s_cuda_encoder_forward_prepared per call for fixed weights),
+    // decoderForward -> dl4s_cuda_decoder_forward, prepareInputs -> dl4s_cuda_embed_positional, the output head of
+    // Transformer.callAsFunction -> dl4s_cuda_output_head, greedy decoding -> dl4s_cuda_transformer_greedy_decode,
+    // Dropout -> dl4s_cuda_set_dropout(rate, seed) before the fused calls: same pattern.
+
+    /// MultiHeadAttention whose heads are spread over the ranks of a communicator (one process per GPU). The library
+    /// issues the all-gather itself; `CUDA.joinCommunicator(rank:world:id:)` wraps dl4s_cuda_comm_unique_id /
+    /// dl4s_cuda_comm_init. `wq/wk/wv` are this rank's column slices, `result` the batch rows this rank owns
+    /// (dl4s_cuda_mha_sharded_plan says which).
+    static func multiHeadAttentionSharded(x: ShapedBuffer<Float, CUDA>, heads: Int, keyDim: Int, valueDim: Int,
+                                          wq: ShapedBuffer<Float, CUDA>, wk: ShapedBuffer<Float, CUDA>, wv: ShapedBuffer<Float, CUDA>,
+                                          wo: ShapedBuffer<Float, CUDA>, normScale: ShapedBuffer<Float, CUDA>, normShift: ShapedBuffer<Float, CUDA>,
+                                          keyLengths: Buffer<Int32, CUDA>?, causal: Bool, chunks: Int, result: ShapedBuffer<Float, CUDA>) {
+        let (B, S, D) = (x.shape[0], x.shape[1], x.shape[2])
+        check(dl4s_cuda_mha_forward_sharded(x.values.memory.floats(), Int64(B), Int64(S), Int64(D), Int64(heads), Int64(keyDim),
+                                            Int64(valueDim), wq.values.memory.floats(), wk.values.memory.floats(),
+                                            wv.values.memory.floats(), wo.values.memory.floats(), normScale.values.memory.floats(),
+                                            normShift.values.memory.floats(),
+                                            keyLengths?.memory.pointer?.assumingMemoryBound(to: Int32.self), causal ? 1 : 0,
+                                            result.values.memory.floats(), CUDA.precision, Int32(chunks)))
+    }
 
     /// One step of incremental decoding. `kCache` / `vCache` are [B, H, maxLength, d]; `lengths` holds the tokens
     /// cached per sequence and is advanced by the caller after the call.

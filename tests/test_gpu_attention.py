@@ -77,6 +77,19 @@ def test_padding_and_causal(dev, oracle, prec, B, H, S, d):
           oracle.sdpa(q, k, v, oracle.make_decoder_mask(np.full(B, S, np.int32), S)), "causal only")
 
 
+def test_many_items_per_resident_cta(dev, oracle):
+    """64-wide heads with a padding mask take the persistent kernel; 1152 (query block, batch x head) items over at most
+    296 resident CTAs make every CTA walk 3-4 items with different key-tile counts (1-3), a blocked sequence and a full
+    one among them: Q buffers, barrier phases and the output accumulator are reused across items."""
+    rng = np.random.default_rng(21)
+    B, H, S, d = 48, 8, 320, 64
+    q, k, v = rand_qkv(rng, B, H, S, S, d, d)
+    lens = rng.integers(1, S + 1, size=B).astype(np.int32)
+    lens[0], lens[1], lens[2], lens[3] = S, 0, 128, 129
+    got = run_sdpa(dev, q, k, v, dev.makeEncoderMasks(lens), PREC_F16)
+    check(PREC_F16, got, oracle.sdpa(q, k, v, oracle.make_encoder_mask(lens, S)), "persistent form, ragged lengths")
+
+
 @pytest.mark.parametrize("prec", [PREC_FP32, PREC_F16], ids=["fp32", "f16"])
 def test_fully_blocked_sequence_is_uniform(dev, prec):
     """The reference subtracts a finite 1e9, so a sequence of length 0 averages ALL value rows."""

@@ -108,3 +108,38 @@ def test_encoder_full_size(dev, oracle, prec):
         assert ma <= TC_MAX_ABS and ma_c <= TC_MAX_ABS, (ma, ma_c)
     else:
         assert ma <= F16_DEEP_MAX_ABS_DOCUMENTED and ma_c <= F16_DEEP_MAX_ABS_DOCUMENTED, (ma, ma_c)
+
+
+def test_head_sharded_layer_full_width(dev):
+    """The head-sharded decoder self-attention layer at its full sequence length, model width and head count (S 2048,
+    D 4096, 32 heads of 128, causal), two batch elements instead of 256: batch elements are independent (the LayerNorm
+    inside MultiHeadAttention is per batch element), so one of them checked against a float64 evaluation of the whole
+    layer is a full-size check of everything but the batch loop. Runs through dl4s_cuda_mha_forward_sharded with a
+    world of one (same kernels and chunking as the multi-GPU runs, no collective)."""
+    from dl4s_b200 import sharded
+    from dl4s_b200.layers import xavier_uniform
+    B, S, D, H = 2, 2048, 4096, 32
+    dk = D // H
+    rw = np.random.default_rng(0)
+    w = {n: xavier_uniform(rw, D, D) for n in ("qDense", "kDense", "vDense", "fc")}
+    x = np.random.default_rng(1).standard_normal((B, S, D), dtype=np.float32)
+    layer = sharded.HeadShardedMultiHeadAttention(H, D, dk, dk, w, precision=PREC_F16, chunks=2)
+    got = layer(dev.tensor(x), dev.StructuredMask(None, causal=True)).numpy()
+    assert got.shape == (B, S, D) and np.isfinite(got).all()
+    # float64, batch element 1, head by head (the [S,S] scores of one head at a time)
+    xb = x[1].astype(np.float64)
+    q, k, v = (xb @ w[n].astype(np.float64) for n in ("qDense", "kDense", "vDense"))
+    heads = np.empty((S, D))
+    blocked = np.triu(np.ones((S, S), bool), 1)
+    for h in range(H):
+        sl = slice(h * dk, (h + 1) * dk)
+        s = (q[:, sl] / np.sqrt(np.float64(dk))) @ k[:, sl].T
+        s[blocked] -= 1e9
+        e = np.exp(s - s.max(axis=1, keepdims=True))
+        heads[:, sl] = (e / e.sum(axis=1, keepdims=True)) @ v[:, sl]
+    z = heads @ w["fc"].astype(np.float64) + xb
+    m = z.mean()
+    want = (z - m) / (np.sqrt((z * z).mean() - m * m) + 1e-5)        # LayerNorm over the whole [S, D] block, scale 1, shift 0
+    ma, rl = max_abs(got[1], want), rel_l2(got[1], want)
+    print(f"head-sharded layer, S {S}, D {D}, {H} heads, batch element 1 of {B}: max-abs {ma:.3e}, rel-L2 {rl:.3e}")
+    assert_tc(got[1], want, "head-sharded layer at full width against float64")

@@ -35,11 +35,13 @@ namespace dl4s {
 // the residual stream.
 constexpr bool kSplitValueOnly = true;
 
-// fp32 [rows, na] | [rows, nb] | [rows, nc] -> half [rows, na+nb+nc] (b, c optional);
+// fp32 [rows, na] | [rows, nb] | [rows, nc] -> half [rows, na+nb+nc] (b, c optional); the first block is multiplied
+// by a_scale before it is rounded (Wq carries the log2(e)/temperature factor of the scores, so the projection's
+// epilogue has nothing to multiply);
 // lo_off != 0: the half-rounded remainders go `lo_off` elements further (the split form).
 __global__ void __launch_bounds__(256) k_concat_cols_f16(const float *__restrict__ a, int na, const float *__restrict__ b, int nb,
                                                          const float *__restrict__ c, int nc, int64_t rows, __half *__restrict__ out,
-                                                         int64_t lo_off, int32_t *status)
+                                                         int64_t lo_off, float a_scale, int32_t *status)
 {
     pdl_launch_dependents();
     pdl_wait();
@@ -56,6 +58,7 @@ __global__ void __launch_bounds__(256) k_concat_cols_f16(const float *__restrict
         else if (col < na + nb) src = b + r * nb + (col - na);
         else src = c + r * nc + (col - na - nb);
         float4 v = *reinterpret_cast<const float4 *>(src);
+        if (col < na) { v.x *= a_scale; v.y *= a_scale; v.z *= a_scale; v.w *= a_scale; }
         uint2 hi, lo;
         split_hilo(v, hi, lo);
         bad |= half2_not_finite(hi.x) | half2_not_finite(hi.y);
@@ -66,7 +69,7 @@ __global__ void __launch_bounds__(256) k_concat_cols_f16(const float *__restrict
 }
 
 static dl4s_status concat_cols_f16(DeviceState *st, const float *a, int na, const float *b, int nb, const float *c, int nc,
-                                   int64_t rows, void *out, int split)
+                                   int64_t rows, void *out, int split, float a_scale)
 {
     DL4S_REQUIRE(na % 4 == 0 && nb % 4 == 0 && nc % 4 == 0, "column counts must be multiples of 4");
     int64_t total = rows * ((na + nb + nc) / 4);
@@ -76,7 +79,7 @@ static dl4s_status concat_cols_f16(DeviceState *st, const float *a, int na, cons
     if (blocks < 1) blocks = 1;
     const int64_t lo_off = split ? rows * (na + nb + nc) : 0;
     DL4S_CUDA_TRY(launch_pdl(st, k_concat_cols_f16, dim3((unsigned)blocks), dim3(256), 0, 1, a, na, b, nb, c, nc, rows, (__half *)out,
-                             lo_off, st->status_word));
+                             lo_off, a_scale, st->status_word));
     return after_launch(st, "k_concat_cols_f16");
 }
 
@@ -98,6 +101,7 @@ struct LayerWeightsArgs {
     int64_t off_wo, off_w1, off_w2;   // destination byte offsets inside a layer
     int D, Nq, Nv, F;
     int split;
+    float q_scale;           // Wq is multiplied by it before rounding (see k_concat_cols_f16)
     int32_t *status;
 };
 
@@ -118,12 +122,13 @@ __global__ void __launch_bounds__(256) k_layer_weights_f16(LayerWeightsArgs a)
         const float *s;
         __half *d;
         int64_t lo_off;   // elements from a matrix's rounded values to its remainders
+        float scale = 1.0f;
         if (i < g_qkv) {
             // 32-bit index arithmetic: the q/k/v block of one layer has far fewer than 2^31 groups
             const unsigned per_row = (unsigned)(nqkv / 4);
             const unsigned r = (unsigned)i / per_row;
             const int col = (int)((unsigned)i - r * per_row) * 4;
-            if (col < a.Nq) s = wq + (int64_t)r * a.Nq + col;
+            if (col < a.Nq) { s = wq + (int64_t)r * a.Nq + col; scale = a.q_scale; }
             else if (col < 2 * a.Nq) s = wk + (int64_t)r * a.Nq + (col - a.Nq);
             else s = wv + (int64_t)r * a.Nv + (col - 2 * a.Nq);
             d = reinterpret_cast<__half *>(dst) + (int64_t)r * nqkv + col;
@@ -145,6 +150,7 @@ __global__ void __launch_bounds__(256) k_layer_weights_f16(LayerWeightsArgs a)
             lo_off = (int64_t)a.D * a.F;
         }
         float4 v = *reinterpret_cast<const float4 *>(s);
+        v.x *= scale; v.y *= scale; v.z *= scale; v.w *= scale;
         uint2 hi, lo;
         split_hilo(v, hi, lo);
         bad |= half2_not_finite(hi.x) | half2_not_finite(hi.y);
@@ -217,7 +223,7 @@ static dl4s_status mha_tc_run(DeviceState *st, const float *xq, const float *xk,
     const int Nq = (int)(H * dk), Nv = (int)(H * dv);
     const float q_scale = attn_prefill_tc_q_scale(1.0f / sqrtf((float)dk));
     if (!have_w) {
-        DL4S_TRY(concat_cols_f16(st, wq, Nq, wk, Nq, wv, Nv, D, m.wqkv_h, split));
+        DL4S_TRY(concat_cols_f16(st, wq, Nq, wk, Nq, wv, Nv, D, m.wqkv_h, split, q_scale));
         DL4S_TRY(weight_to_f16(st, wo, m.wo_h, H * dv * D, split));
     }
     if (!have_xh) {
@@ -234,7 +240,6 @@ static dl4s_status mha_tc_run(DeviceState *st, const float *xq, const float *xk,
         o.nparts = 3; o.S = (int)Sq;
         o.part_ptr[0] = m.qh; o.part_ptr[1] = m.kh; o.part_ptr[2] = m.vh;
         o.part_d[0] = (int)dk; o.part_d[1] = (int)dk; o.part_d[2] = (int)dv;
-        o.part_scale[0] = q_scale;
         DL4S_TRY(launch_gemm_tc_h(st, m.xq_h, m.wqkv_h, B * Sq, 2 * Nq + Nv, D, EPI_NONE, nullptr, nullptr, o, 1, 0, split, nullptr,
                                   kSplitValueOnly ? 2 * Nq : 0));
     } else {
@@ -348,7 +353,7 @@ dl4s_status mha_heads_self_tc(DeviceState *st, const float *x, int64_t B, int64_
     DL4S_TRY(arena_reserve(st, need, &base));
     Bump bp(base);
     layout(bp, &w, &xh, &qh, &kh, &vh);
-    DL4S_TRY(concat_cols_f16(st, wq, Nq, wk, Nq, wv, Nv, D, w, split));
+    DL4S_TRY(concat_cols_f16(st, wq, Nq, wk, Nq, wv, Nv, D, w, split, attn_prefill_tc_q_scale(1.0f / sqrtf((float)dk))));
     if (x_half) xh = const_cast<void *>(x_half);
     else DL4S_TRY(launch_f32_to_f16(st, x, xh, B * S * D));
     GemmTcOut o;
@@ -356,7 +361,6 @@ dl4s_status mha_heads_self_tc(DeviceState *st, const float *x, int64_t B, int64_
     o.H = (int)H; o.S = (int)S; o.nparts = 3;
     o.part_ptr[0] = qh; o.part_ptr[1] = kh; o.part_ptr[2] = vh;
     o.part_d[0] = (int)dk; o.part_d[1] = (int)dk; o.part_d[2] = (int)dv;
-    o.part_scale[0] = attn_prefill_tc_q_scale(1.0f / sqrtf((float)dk));
     DL4S_TRY(launch_gemm_tc_h(st, xh, w, B * S, 2 * Nq + Nv, D, EPI_NONE, nullptr, nullptr, o, 1, 0, split, nullptr,
                               kSplitValueOnly ? 2 * Nq : 0));
     return launch_attn_prefill_tc_h(st, qh, kh, vh, out, strides_bshd(H, S, dv), out_half, B, H, S, S, dk, mask);
@@ -477,7 +481,7 @@ static void layer_param_pointers(const float *params, LayerP *lp, int64_t D, int
 
 // All weights of all layers to half (one launch).
 static dl4s_status convert_layer_weights(DeviceState *st, const float *params, const LayerW *lw, int64_t D, int64_t Nq, int64_t Nv,
-                                         int64_t F, int64_t layers, int split)
+                                         int64_t F, int64_t layers, int split, float q_scale)
 {
     DL4S_REQUIRE(((uintptr_t)params & 15) == 0, "the parameter block must be 16-byte aligned");
     DL4S_REQUIRE(D % 4 == 0 && Nq % 4 == 0 && Nv % 4 == 0 && F % 4 == 0, "weight extents must be multiples of 4");
@@ -491,6 +495,7 @@ static dl4s_status convert_layer_weights(DeviceState *st, const float *params, c
     a.off_w2 = static_cast<char *>(lw[0].w2_h) - a.dst;
     a.D = (int)D; a.Nq = (int)Nq; a.Nv = (int)Nv; a.F = (int)F;
     a.split = split;
+    a.q_scale = q_scale;
     a.status = st->status_word;
     DL4S_REQUIRE(D * (2 * Nq + Nv) / 4 < (1ll << 31), "projection weights too large for the conversion kernel's index arithmetic");
     int64_t groups = (D * (2 * Nq + Nv) + Nv * D + 2 * D * F) / 4;
@@ -538,7 +543,7 @@ static dl4s_status encoder_tc_run(DeviceState *st, const float *x, int64_t B, in
 
     LayerP lp[kMaxLayers];
     layer_param_pointers(params, lp, D, Nq, Nv, F, layers);
-    if (!prep) DL4S_TRY(convert_layer_weights(st, params, lw, D, Nq, Nv, F, layers, split));
+    if (!prep) DL4S_TRY(convert_layer_weights(st, params, lw, D, Nq, Nv, F, layers, split, attn_prefill_tc_q_scale(1.0f / sqrtf((float)dk))));
     DL4S_TRY(launch_f32_to_f16(st, x, xh, M * D));
     const float *cur = x;
     for (int64_t l = 0; l < layers; ++l) {
@@ -582,7 +587,8 @@ dl4s_status encoder_prepare(DeviceState *st, int64_t D, int64_t H, int64_t dk, i
     }
     Bump bp(p->block);
     layer_weights_layout(bp, p->lw, D, H * dk, H * dv, F, layers, split);
-    dl4s_status s = convert_layer_weights(st, params, p->lw, D, H * dk, H * dv, F, layers, split);
+    dl4s_status s = convert_layer_weights(st, params, p->lw, D, H * dk, H * dv, F, layers, split,
+                                          attn_prefill_tc_q_scale(1.0f / sqrtf((float)dk)));
     if (s != DL4S_OK) {
         cudaFree(p->block);
         delete p;
@@ -610,7 +616,8 @@ dl4s_status encoder_prepared_refresh(DeviceState *st, void *handle)
 {
     EncoderPrepared *p = as_prepared(st, handle);
     if (!p) return DL4S_ERR_INVALID_ARG;
-    return convert_layer_weights(st, p->params, p->lw, p->D, p->H * p->dk, p->H * p->dv, p->F, p->layers, p->split);
+    return convert_layer_weights(st, p->params, p->lw, p->D, p->H * p->dk, p->H * p->dv, p->F, p->layers, p->split,
+                                 attn_prefill_tc_q_scale(1.0f / sqrtf((float)p->dk)));
 }
 
 dl4s_status encoder_prepared_destroy(DeviceState *st, void *handle)

@@ -38,9 +38,11 @@
 //   * the half-output flavours read their whole share of the accumulator into registers, hand it back, and only
 //     then convert and store (the accumulator is held ~1000 cycles instead of ~5000);
 //   * the first tile's loads are issued before anything else the producer does.
-// After that the half-output flavours at K = 512 are bound by the epilogue warps' instruction issue (~1000
-// instructions per warp and tile, issue slots 46 % busy with 4 warps per scheduler, ~5000-5500 cycles per tile
-// against a 4300-cycle pair main loop): single-CTA and two-CTA tiles then run at the same rate, and short
+// After that the half-output flavours at K = 512 run their epilogue in ~5000-5500 cycles per tile against a
+// 4300-cycle pair main loop (issue slots 46 % busy with 4 warps per scheduler, ~1000 instructions per warp and
+// tile). Making the epilogue lighter (the score scale folded into Wq when it is rounded, the half-range check as a
+// running maximum, fewer shuffles) moved the step by < 1 %, and two-CTA tiles at K = 512 by another 1 % in one mode
+// and nothing in the other: single-CTA and two-CTA tiles run at practically the same rate there, and short
 // products keep the single-CTA kernel.
 // Every mbarrier wait is bounded; on expiry the kernel sets the device status
 // word and unwinds through the common exit, which frees the tensor memory.
@@ -72,6 +74,14 @@ __device__ __forceinline__ float gelu_sigmoid_tc(float t)
     float e;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t * -2.4554669595930157f));
     return __fdividef(t, 1.0f + e);
+}
+
+// max(m, |a|, |b|) in one instruction.
+__device__ __forceinline__ float max3_abs(float m, float a, float b)
+{
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(m), "f"(fabsf(a)), "f"(fabsf(b)));
+    return d;
 }
 
 // fp32 -> half, 8 elements per thread per step.
@@ -175,11 +185,10 @@ struct GemmTcParams {
     uint32_t wait_polls;     // poll limit of every bounded wait (kWaitPolls; short under an injected fault)
     int a_groups;            // column groups of A; the k walk wraps to group 0 after the last one (split B: K = 2 x A's width)
     // OUT_HEADS_F16: columns [part_begin[p], part_begin[p+1]) go to part_ptr[p], a half tensor
-    // [B, H, S, part_d[p]] (row m = b*S + s), multiplied by part_scale[p].
+    // [B, H, S, part_d[p]] (row m = b*S + s).
     __half *part_ptr[3];
     int part_begin[4];
     int part_d[3];
-    float part_scale[3];
     int S, H;
 };
 
@@ -482,7 +491,7 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                 my_ss = (int)(my_row - (uint32_t)my_bb * (uint32_t)p.S);
             }
             float stat1 = 0.f, stat2 = 0.f;   // EPI_RESIDUAL_STATS: this lane's share of the warp's block
-            bool half_overflow = false;       // half outputs: a result outside the half range
+            float amax = 0.f;                 // half outputs: largest magnitude this lane converts (range check at the end)
             constexpr bool kHasResidual = (EPI == EPI_BIAS_RESIDUAL || EPI == EPI_RESIDUAL || EPI == EPI_RESIDUAL_STATS);
             // Head-major output, common case: the warp's 32 rows lie in one batch element, so the rows a lane
             // stores (rsub, rsub + 8, ...) are part_d * 8 elements apart and one address per group is enough.
@@ -521,16 +530,15 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                 // The next 32 columns travel from tensor memory while this group is written out.
                 if (has_next) load_group(rnx, c0 + 32);
                 if (col0 >= p.N) return;   // N is a multiple of 64: a 32-column group is all in or all out
-                // Half outputs: the four lanes of a row hold, after conversion, one half2 at columns 8p + 2j (p = 0..3,
-                // j = lane % 4). A 4 x 4 transpose among them (two shuffle rounds) leaves lane j with the eight
-                // consecutive columns 8j .. 8j+7, one 16-byte store per row: a warp store then covers 8 rows x 64
-                // contiguous bytes, half as many store instructions (and line visits in the load/store unit) as
-                // 8-byte stores, which is what the epilogue's length was made of. ch = first column this lane stores.
-                const int ch = (lane & 3) * 8;
+                // Half outputs: two lanes that hold neighbouring column pairs swap one pair each, so that every lane
+                // stores 4 consecutive halves (8 bytes) and the four lanes of a row 32 contiguous bytes: whole
+                // sectors. (A 4 x 4 transpose to one 16-byte store per lane halves the store count but costs more
+                // shuffles and selects than it saves; the epilogue is bound by its instruction count.)
+                // ch = first of the 4 columns (within 8) this lane then stores.
+                const int ch = ((lane >> 1) & 1) * 4;
                 // Head-major output: the 32-column group lies inside one head of one part.
                 __half *part_base = nullptr;
                 int part_d = 1, head = 0, dcol = 0;
-                float scale = 1.0f;
                 __half *hdst = nullptr;       // half outputs: address of this lane's first row, then a constant step
                 int64_t hstep = 0;
                 if (OUT == OUT_HEADS_F16) {
@@ -540,7 +548,6 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                     head = rel / part_d;
                     dcol = rel - head * part_d + ch;
                     part_base = p.part_ptr[part];
-                    scale = p.part_scale[part];
                     hdst = part_base + (((int64_t)bb_first * p.H + head) * p.S + ss_first + rsub) * part_d + dcol;
                     hstep = (int64_t)8 * part_d;
                 } else if (OUT == OUT_F16) {
@@ -604,23 +611,21 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                         if (OUT == OUT_F32) {
                             if (row_ok) *reinterpret_cast<float2 *>(fdst + (int64_t)rq * 8 * p.N + pp * 8) = t;
                         } else {
-                            __half2 h = __floats2half2_rn(t.x * scale, t.y * scale);
+                            __half2 h = __floats2half2_rn(t.x, t.y);
                             h2[pp] = *reinterpret_cast<uint32_t *>(&h);
-                            half_overflow |= half2_not_finite(h2[pp]);
+                            amax = max3_abs(amax, t.x, t.y);
                         }
                     }
                     if (OUT != OUT_F32) {
-                        const bool odd = lane & 1, hi = lane & 2;
-                        const uint32_t r0 = __shfl_xor_sync(0xffffffffu, odd ? h2[0] : h2[1], 1);
-                        const uint32_t r1 = __shfl_xor_sync(0xffffffffu, odd ? h2[2] : h2[3], 1);
-                        const uint32_t a0 = odd ? r0 : h2[0], a1 = odd ? h2[1] : r0;
-                        const uint32_t a2 = odd ? r1 : h2[2], a3 = odd ? h2[3] : r1;
-                        const uint32_t q0 = __shfl_xor_sync(0xffffffffu, hi ? a0 : a2, 2);
-                        const uint32_t q1 = __shfl_xor_sync(0xffffffffu, hi ? a1 : a3, 2);
-                        uint4 o;
-                        o.x = hi ? q0 : a0; o.y = hi ? q1 : a1;
-                        o.z = hi ? a2 : q0; o.w = hi ? a3 : q1;
-                        if (row_ok) *reinterpret_cast<uint4 *>(hrow) = o;
+#pragma unroll
+                        for (int p2 = 0; p2 < 4; p2 += 2) {
+                            const uint32_t send = (lane & 1) ? h2[p2] : h2[p2 + 1];
+                            const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                            uint2 o;
+                            o.x = (lane & 1) ? recv : h2[p2];
+                            o.y = (lane & 1) ? h2[p2 + 1] : recv;
+                            if (row_ok) *reinterpret_cast<uint2 *>(hrow + (p2 + (lane & 1)) * 8) = o;
+                        }
                     }
                 }
             };
@@ -679,7 +684,10 @@ __global__ void __launch_bounds__(gemm_threads(EPI, PAIR), 1) k_gemm_tc(const __
                     p.ln_stats[2 * slot + 1] = d2;
                 }
             }
-            if (OUT != OUT_F32 && half_overflow) atomicOr(p.status, kStatusHalfRange);
+            // 65504 is the largest finite half; anything that rounds beyond it (or an accumulator that is already
+            // infinite) trips the range bit. NaNs cannot appear here without a non-finite operand, and those are
+            // caught where the operands were converted.
+            if (OUT != OUT_F32 && !(amax < 65520.f)) atomicOr(p.status, kStatusHalfRange);
             if (!kEarlyRelease) release_acc();
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
         }
@@ -873,7 +881,7 @@ dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_
     p.out_mode = out.mode;
     p.status = st->status_word;
     p.S = 1; p.H = 1;
-    for (int i = 0; i < 3; ++i) { p.part_ptr[i] = nullptr; p.part_begin[i] = 0; p.part_d[i] = 32; p.part_scale[i] = 1.f; }
+    for (int i = 0; i < 3; ++i) { p.part_ptr[i] = nullptr; p.part_begin[i] = 0; p.part_d[i] = 32; }
     p.part_begin[3] = 0;
     if (out.mode == OUT_HEADS_F16) {
         DL4S_REQUIRE(out.nparts >= 1 && out.nparts <= 3 && out.S >= 1 && M % out.S == 0, "bad head-major output description");
@@ -884,7 +892,6 @@ dl4s_status launch_gemm_tc_h(DeviceState *st, const void *a_half, const void *b_
                 DL4S_REQUIRE(out.part_d[i] % 32 == 0 && ((uintptr_t)out.part_ptr[i] & 15) == 0, "head size must be a multiple of 32");
                 p.part_ptr[i] = (__half *)out.part_ptr[i];
                 p.part_d[i] = out.part_d[i];
-                p.part_scale[i] = out.part_scale[i];
                 begin += out.H * out.part_d[i];
             } else {
                 p.part_begin[i] = 1 << 30;   // never selected
@@ -963,7 +970,7 @@ dl4s_status launch_gemm_tc_trans(DeviceState *st, const float *a, const float *b
     p.out_mode = OUT_F32;
     p.status = st->status_word;
     p.S = 1; p.H = 1;
-    for (int i = 0; i < 3; ++i) { p.part_d[i] = 32; p.part_scale[i] = 1.f; }
+    for (int i = 0; i < 3; ++i) p.part_d[i] = 32;
     if (trans_a && trans_b) return run_gemm_tc_trans<1, 1>(st, ta, tb, p, wide);
     if (trans_a) return run_gemm_tc_trans<1, 0>(st, ta, tb, p, wide);
     return run_gemm_tc_trans<0, 1>(st, ta, tb, p, wide);

@@ -35,7 +35,6 @@ struct GemmTcOut {
     int nparts = 0;
     void *part_ptr[3] = {nullptr, nullptr, nullptr};
     int part_d[3] = {0, 0, 0};
-    float part_scale[3] = {1.f, 1.f, 1.f};
     int S = 1, H = 1;
     double *ln_stats = nullptr;   // EPI_RESIDUAL_STATS
 };

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 
 from oracle import oracle_np as ON
-from util import golden, max_abs, rel_l2, unpack_layers
+from util import golden, golden_next, max_abs, rel_l2, unpack_layers
 
 
 def test_gemm_known_answers_from_reference_tests(oracle):
@@ -246,3 +246,25 @@ def test_layernorm_backward_matches_finite_differences():
             bp[c] += eps
             bm[c] -= eps
             assert abs((loss(x, g, bp) - loss(x, g, bm)) / (2 * eps) - db[c]) < 1e-6
+
+
+def test_golden_vectors_of_the_next_rows(oracle):
+    """The oracle reproduces the frozen backward, embedding and output-head vectors bit for bit (C restatement) and the
+    float64 LayerNorm backward to rounding."""
+    from oracle import oracle_np as ON
+    g = golden_next()
+    q, k, v, d = g["bwd_q"], g["bwd_k"], g["bwd_v"], g["bwd_dout"]
+    for name, mask in (("pad", oracle.make_encoder_mask(g["bwd_lens"], 6)), ("dec", oracle.make_decoder_mask(g["bwd_lens"], 6))):
+        dq, dk, dv = oracle.sdpa_backward(q, k, v, d, mask)
+        assert np.array_equal(dq, g[f"bwd_{name}_dq"]) and np.array_equal(dk, g[f"bwd_{name}_dk"])
+        assert np.array_equal(dv, g[f"bwd_{name}_dv"])
+        # and the float64 closed form agrees with the frozen fp32 values
+        wq, wk, wv = ON.sdpa_backward(q, k, v, d, mask)
+        assert max_abs(dq, wq) < 1e-5 and max_abs(dk, wk) < 1e-5 and max_abs(dv, wv) < 1e-5
+    x = oracle.embed(g["emb_ids"], g["emb_E"])
+    assert np.array_equal(x, g["emb_out"])
+    assert np.array_equal(x[0, 2], oracle.positional_encoding(5, 16)[2])          # an ignored index embeds as zeros + position
+    assert np.array_equal(oracle.output_head(x, g["emb_E"], g["head_bias"]), g["head_out"])
+    assert np.allclose(np.exp(g["head_out"].astype(np.float64)).sum(axis=-1), 1.0, atol=1e-5)
+    dx, ds, db = ON.layernorm_backward(g["lnb_x"], g["lnb_dy"], g["lnb_scale"])
+    assert max_abs(dx, g["lnb_dx"]) < 1e-12 and max_abs(ds, g["lnb_dscale"]) < 1e-12 and max_abs(db, g["lnb_dshift"]) < 1e-12

@@ -16,6 +16,11 @@ def golden():
     return np.load(GOLDEN)
 
 
+def golden_next():
+    """The second fixture file: backward, embedding and output-head rows (tests/golden/make_golden_next.py)."""
+    return np.load(os.path.join(os.path.dirname(GOLDEN), "hotpath_next.npz"))
+
+
 def rel_l2(a, b):
     a = np.asarray(a, np.float64)
     b = np.asarray(b, np.float64)

@@ -131,13 +131,12 @@ static int make_plan(int64_t B, int world, int rank, int chunks, ChunkPlan *plan
     return chunks;
 }
 
-// dl4s_cuda_shutdown: the device's membership goes with its state (device current, stream already idle).
-void comm_release_device(int ordinal)
+// Everything a CommState owns; leaves it in its initial state. Returns what ncclCommDestroy said.
+static dl4s_status comm_release(CommState &c)
 {
-    CommState &c = g_comm[ordinal];
-    if (!c.live && !c.gather && !c.xh) return;
     if (c.stream) cudaStreamSynchronize(c.stream);
-    if (c.comm && g_nccl.comm_destroy) g_nccl.comm_destroy(c.comm);
+    dl4s_status result = DL4S_OK;
+    if (c.comm && g_nccl.comm_destroy) result = nccl_check(g_nccl.comm_destroy(c.comm), "ncclCommDestroy");
     for (int i = 0; i < kMaxChunks; ++i) {
         cudaEvent_t evs[4] = {c.ready[i], c.done[i], c.wait0[i], c.wait1[i]};
         for (cudaEvent_t e : evs) if (e) cudaEventDestroy(e);
@@ -146,6 +145,15 @@ void comm_release_device(int ordinal)
     if (c.gather) cudaFree(c.gather);
     if (c.xh) cudaFree(c.xh);
     c = CommState();
+    return result;
+}
+
+// dl4s_cuda_shutdown: the device's membership goes with its state (device current, stream already idle).
+void comm_release_device(int ordinal)
+{
+    CommState &c = g_comm[ordinal];
+    if (!c.live && !c.gather && !c.xh && !c.stream && !c.comm) return;
+    comm_release(c);
 }
 
 }  // namespace dl4s
@@ -185,15 +193,24 @@ dl4s_status dl4s_cuda_comm_init(int32_t rank, int32_t world, const uint8_t *id)
     if (world > 1) {
         DL4S_REQUIRE(id, "id is NULL");
         DL4S_TRY(nccl_load());
-        NcclUniqueId u;
-        memcpy(u.internal, id, DL4S_COMM_ID_BYTES);
-        DL4S_TRY(nccl_check(g_nccl.comm_init_rank(&c.comm, world, u, rank), "ncclCommInitRank"));
-        DL4S_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
-        for (int i = 0; i < kMaxChunks; ++i) {
-            DL4S_CUDA_TRY(cudaEventCreate(&c.ready[i]));
-            DL4S_CUDA_TRY(cudaEventCreate(&c.done[i]));
-            DL4S_CUDA_TRY(cudaEventCreate(&c.wait0[i]));
-            DL4S_CUDA_TRY(cudaEventCreate(&c.wait1[i]));
+        // anything that fails from here on releases what has been created so far
+        auto create = [&]() -> dl4s_status {
+            NcclUniqueId u;
+            memcpy(u.internal, id, DL4S_COMM_ID_BYTES);
+            DL4S_TRY(nccl_check(g_nccl.comm_init_rank(&c.comm, world, u, rank), "ncclCommInitRank"));
+            DL4S_CUDA_TRY(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+            for (int i = 0; i < kMaxChunks; ++i) {
+                DL4S_CUDA_TRY(cudaEventCreate(&c.ready[i]));
+                DL4S_CUDA_TRY(cudaEventCreate(&c.done[i]));
+                DL4S_CUDA_TRY(cudaEventCreate(&c.wait0[i]));
+                DL4S_CUDA_TRY(cudaEventCreate(&c.wait1[i]));
+            }
+            return DL4S_OK;
+        };
+        const dl4s_status r = create();
+        if (r != DL4S_OK) {
+            comm_release(c);
+            return r;
         }
     }
     c.live = true;
@@ -206,18 +223,7 @@ dl4s_status dl4s_cuda_comm_destroy(void)
     CommState &c = g_comm[st->ordinal];
     if (!c.live && !c.gather && !c.xh) return DL4S_OK;
     cudaStreamSynchronize(st->stream);
-    if (c.stream) cudaStreamSynchronize(c.stream);
-    dl4s_status result = DL4S_OK;
-    if (c.comm) result = nccl_check(g_nccl.comm_destroy(c.comm), "ncclCommDestroy");
-    for (int i = 0; i < kMaxChunks; ++i) {
-        cudaEvent_t evs[4] = {c.ready[i], c.done[i], c.wait0[i], c.wait1[i]};
-        for (cudaEvent_t e : evs) if (e) cudaEventDestroy(e);
-    }
-    if (c.stream) cudaStreamDestroy(c.stream);
-    if (c.gather) cudaFree(c.gather);
-    if (c.xh) cudaFree(c.xh);
-    c = CommState();
-    return result;
+    return comm_release(c);
 }
 
 dl4s_status dl4s_cuda_comm_info(int32_t *rank, int32_t *world, int32_t *nccl_version)
